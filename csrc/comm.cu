@@ -1,0 +1,535 @@
+#include "comm.h"
+
+#include <string.h>
+
+#include <algorithm>
+#include <stdexcept>
+
+#include "all_reduce_oneshot.cuh"
+#include "all_reduce_ring.cuh"
+#include "all_reduce_tree.cuh"
+#include "all_reduce_twoshot.cuh"
+#include "exchange.cuh"
+#include "launch.cuh"
+
+namespace penny {
+
+namespace {
+void ckrt(cudaError_t r, const char* what) {
+  if (r != cudaSuccess) {
+    (void)cudaGetLastError();
+    throw std::runtime_error(std::string("penny: ") + what + ": " + cudaGetErrorString(r));
+  }
+}
+constexpr size_t kScratchCap = (size_t)512 << 20;  // a single call never asks for more
+}  // namespace
+
+Communicator::Communicator(const std::string& uid, int rank, int world, const CommOptions& opt)
+    : rank_(rank), world_(world), emu_(false) {
+  bs_.reset(new Bootstrap(uid, rank, world, opt.bootstrap_timeout_ms));
+  heap_.reset(new SymmHeap(bs_.get(), rank, world, opt.heap_bytes, opt.heap_mode, opt.multicast));
+  init_ctx(opt);
+}
+
+Communicator::Communicator(int emu_world, const CommOptions& opt)
+    : rank_(0), world_(emu_world), emu_(true) {
+  heap_.reset(new SymmHeap(nullptr, 0, emu_world, opt.heap_bytes, HEAP_EMU, false));
+  init_ctx(opt);
+}
+
+Communicator::~Communicator() {
+  try {
+    destroy();
+  } catch (...) {
+  }
+}
+
+void Communicator::init_ctx(const CommOptions& opt) {
+  memset(&ctx_, 0, sizeof(ctx_));
+  for (int r = 0; r < world_; ++r) ctx_.heap[r] = heap_->base(r);
+  ctx_.mc = heap_->mc_base();
+  ctx_.rank = rank_;
+  ctx_.world = world_;
+  ctx_.timeout_ns = (unsigned long long)opt.timeout_ms * 1000000ull;
+  ctx_.status = reinterpret_cast<uint32_t*>(heap_->base(rank_) + kStatusOffset);
+  if (heap_->bytes() < kHeapReserved + (1u << 20))
+    throw std::runtime_error("penny: heap too small");
+}
+
+void Communicator::destroy() {
+  if (destroyed_) return;
+  destroyed_ = true;
+  if (heap_) heap_->destroy();
+}
+
+std::string Communicator::describe() const {
+  static const char* modes[] = {"auto", "vmm", "ipc", "emu"};
+  return std::string("penny communicator rank ") + std::to_string(rank_) + "/" +
+         std::to_string(world_) + " heap=" + modes[heap_->mode()] + " " +
+         std::to_string(heap_->bytes() >> 20) + " MiB, multicast: " + heap_->multicast_note();
+}
+
+void Communicator::set_timeout_ms(int ms) {
+  ctx_.timeout_ns = (unsigned long long)ms * 1000000ull;
+}
+
+size_t Communicator::alloc(size_t bytes) {
+  size_t off = round_up(arena_top_, 256);
+  size_t end = off + round_up(bytes, 256);
+  if (end > heap_->bytes())
+    throw std::runtime_error("penny: symmetric heap exhausted (" + std::to_string(bytes) +
+                             " bytes requested, " + std::to_string(heap_->bytes() - arena_top_) +
+                             " free); raise heap_bytes / PENNY_HEAP_BYTES");
+  arena_top_ = end;
+  return off;
+}
+
+void* Communicator::local_ptr(size_t off, int view) const {
+  return heap_->base(emu_ ? view : rank_) + off;
+}
+
+size_t Communicator::heap_offset_of(const void* p, int view) const {
+  const char* b = heap_->base(emu_ ? view : rank_);
+  const char* c = reinterpret_cast<const char*>(p);
+  if (c >= b + kHeapReserved && c < b + heap_->bytes()) return (size_t)(c - b);
+  return kNotInHeap;
+}
+
+Communicator::Region& Communicator::ensure(Region& r, size_t need, const char* what) {
+  need = round_up(need, 512);
+  if (r.bytes >= need) return r;
+  size_t want = std::max(need, std::min(r.bytes * 2, kScratchCap));
+  size_t free_b = heap_free_bytes();
+  if (want + 512 > free_b) want = need;
+  try {
+    r.off = alloc(want);
+  } catch (const std::exception& e) {
+    throw std::runtime_error(std::string(e.what()) + " [while growing " + what + " scratch]");
+  }
+  r.bytes = want;
+  return r;
+}
+
+LaunchCfg Communicator::cfg_for(size_t vecs, const Tuning& t, cudaStream_t s, int max_blocks,
+                                int multiple) const {
+  LaunchCfg cfg;
+  cfg.threads = t.threads > 0 ? t.threads : 512;
+  cfg.stream = s;
+  cfg.emu_world = emu_ ? world_ : 0;
+  // emulation: all virtual ranks' blocks must be co-resident (one 512-thread
+  // block per SM in the worst case)
+  if (emu_) max_blocks = std::max(1, std::min(max_blocks, 128 / world_));
+  max_blocks = std::min(max_blocks, kMaxBlocks);
+  int blocks = t.blocks;
+  if (blocks <= 0) {
+    size_t per_block = (size_t)cfg.threads * 4;
+    blocks = (int)std::min<size_t>((size_t)max_blocks, std::max<size_t>(1, ceil_div(vecs, per_block)));
+  }
+  blocks = std::min(blocks, max_blocks);
+  if (multiple > 1) {
+    blocks = std::max(multiple, blocks / multiple * multiple);
+    if (blocks > max_blocks && max_blocks >= multiple) blocks = max_blocks / multiple * multiple;
+  }
+  cfg.blocks = blocks;
+  return cfg;
+}
+
+int Communicator::pick_algo(int dtype, size_t n) const {
+  const size_t bytes = n * (size_t)dtype_size(dtype);
+  if (world_ < 2) return ALGO_ONESHOT;
+  const bool even = (world_ == 2 || world_ == 4 || world_ == 6 || world_ == 8);
+  if (!even) return ALGO_RING_STANDARD;
+  if (bytes <= (size_t)32 << 10) return ALGO_ONESHOT_LL;
+  if (bytes <= (size_t)256 << 10) return ALGO_ONESHOT;
+  if (has_multicast()) return ALGO_NVLS;
+  return ALGO_TWOSHOT;
+}
+
+void Communicator::all_reduce(int algo, int dtype, const void* const* in, void* const* out,
+                              size_t n, const Tuning& t, cudaStream_t stream) {
+  if (n == 0) return;
+  const int es = dtype_size(dtype);
+  if (world_ == 1) {
+    if (in[0] != out[0])
+      ckrt(cudaMemcpyAsync(out[0], in[0], n * es, cudaMemcpyDeviceToDevice, stream), "memcpy");
+    return;
+  }
+  if (algo == ALGO_AUTO) algo = pick_algo(dtype, n);
+  if ((algo == ALGO_NVLS || algo == ALGO_NVLS_ONESHOT) && !has_multicast())
+    throw std::runtime_error("penny: NVLS all-reduce requested but the heap has no multicast (" +
+                             heap_->multicast_note() + ")");
+  // Split so that one launch never needs more scratch than the cap.  Segment
+  // boundaries are multiples of 16 bytes so every segment stays vector-aligned.
+  size_t per_elem_scratch;  // scratch bytes per element (both halves), upper bound
+  switch (algo) {
+    case ALGO_ONESHOT: per_elem_scratch = 2 * (size_t)world_ * es; break;
+    case ALGO_ONESHOT_LL: per_elem_scratch = 4 * (size_t)world_ * es; break;
+    case ALGO_TREE: per_elem_scratch = 2 * (size_t)(2 + t.nnodes) * es; break;
+    case ALGO_NVLS:
+    case ALGO_NVLS_ONESHOT: per_elem_scratch = es; break;  // staging at most
+    default: per_elem_scratch = 4 * (size_t)es; break;
+  }
+  size_t budget = std::min(kScratchCap, std::max<size_t>(heap_free_bytes() / 2, (size_t)1 << 20));
+  if (algo == ALGO_NVLS || algo == ALGO_NVLS_ONESHOT) budget = kScratchCap;
+  size_t seg = std::max<size_t>(budget / per_elem_scratch / 1024 * 1024, 1024);
+  if (n <= seg) {
+    run_all_reduce_once(algo, dtype, in, out, n, t, stream);
+    return;
+  }
+  std::vector<const void*> in_s(views());
+  std::vector<void*> out_s(views());
+  for (size_t o = 0; o < n; o += seg) {
+    for (int v = 0; v < views(); ++v) {
+      in_s[v] = (const char*)in[v] + o * es;
+      out_s[v] = (char*)out[v] + o * es;
+    }
+    run_all_reduce_once(algo, dtype, in_s.data(), out_s.data(), std::min(seg, n - o), t, stream);
+  }
+}
+
+void Communicator::run_all_reduce_once(int algo, int dtype, const void* const* in,
+                                       void* const* out, size_t n, const Tuning& t,
+                                       cudaStream_t stream) {
+  const int es = dtype_size(dtype);
+  const size_t V = vecs_for(n, es);
+  const int nv = views();
+  int nnodes = t.nnodes > 0 ? t.nnodes : 1;
+  if (world_ % nnodes != 0) throw std::runtime_error("penny: nnodes must divide the world size");
+  CollArgs a[kMaxRanks];
+  memset(a, 0, sizeof(a));
+  for (int v = 0; v < nv; ++v) {
+    a[v].in = in[v];
+    a[v].out = out[v];
+    a[v].n = n;
+    a[v].in_heap_off = heap_offset_of(in[v], v);
+    a[v].out_heap_off = kNotInHeap;
+    a[v].nnodes = nnodes;
+    a[v].routes = 1;
+  }
+  auto set_scratch = [&](const Region& r) {
+    for (int v = 0; v < nv; ++v) {
+      a[v].scratch_off = r.off;
+      a[v].scratch_bytes = r.bytes;
+    }
+  };
+  cudaError_t rc = cudaSuccess;
+  switch (algo) {
+    case ALGO_ONESHOT: {
+      set_scratch(ensure(scratch_, oneshot_flag_scratch_bytes(n, es, world_), "one-shot"));
+      rc = launch_all_reduce_oneshot(dtype, false, ctx_, a, cfg_for(V, t, stream, 64, 1));
+      break;
+    }
+    case ALGO_ONESHOT_LL: {
+      set_scratch(ensure(scratch_ll_, oneshot_ll_scratch_bytes(n, es, world_), "LL"));
+      Tuning tt = t;
+      if (tt.threads <= 0) tt.threads = 256;
+      LaunchCfg cfg = cfg_for(V, tt, stream, 64, 1);
+      if (t.blocks <= 0) cfg.blocks = (int)std::min<size_t>(emu_ ? 128 / world_ : 64,
+                                                             std::max<size_t>(1, ceil_div(V, cfg.threads)));
+      rc = launch_all_reduce_oneshot(dtype, true, ctx_, a, cfg);
+      break;
+    }
+    case ALGO_TWOSHOT: {
+      set_scratch(ensure(scratch_, twoshot_scratch_bytes(n, es, world_), "two-shot"));
+      // direct gather only if every rank's output sits at the same heap offset
+      size_t oo = heap_offset_of(out[0], 0);
+      bool same = oo != kNotInHeap && (n * es) % 16 == 0;
+      for (int v = 1; v < nv; ++v) same = same && heap_offset_of(out[v], v) == oo;
+      if (same && t.symmetric_out)
+        for (int v = 0; v < nv; ++v) a[v].out_heap_off = oo;
+      rc = launch_all_reduce_twoshot(dtype, ctx_, a, cfg_for(ceil_div(V, world_), t, stream, 128, 1));
+      break;
+    }
+    case ALGO_RING_SIMPLE: {
+      set_scratch(ensure(scratch_, ring_simple_scratch_bytes(n, es, world_), "ring"));
+      rc = launch_all_reduce_ring_simple(dtype, ctx_, a, cfg_for(V, t, stream, 64, 1));
+      break;
+    }
+    case ALGO_RING_STANDARD: {
+      set_scratch(ensure(scratch_, ring_standard_scratch_bytes(n, es, world_), "ring"));
+      int routes = t.routes > 0 ? t.routes : (V >= 4096 ? std::min(4, num_ring_strides(world_)) : 1);
+      routes = std::min(routes, kMaxRoutes);
+      if (nnodes > 1) routes = std::min(routes, std::max(1, world_ / nnodes));
+      for (int v = 0; v < nv; ++v) a[v].routes = routes;
+      rc = launch_all_reduce_ring_standard(
+          dtype, ctx_, a, cfg_for(ceil_div(V, world_), t, stream, 96, routes));
+      break;
+    }
+    case ALGO_DOUBLE_RING: {
+      LaunchCfg cfg = cfg_for(V, t, stream, 64, 1);
+      set_scratch(ensure(scratch_, double_ring_scratch_bytes(n, es, world_, nnodes, cfg.blocks),
+                         "double ring"));
+      // the slot size is derived from scratch_bytes / blocks: lend exactly what this shape needs
+      for (int v = 0; v < nv; ++v)
+        a[v].scratch_bytes = double_ring_scratch_bytes(n, es, world_, nnodes, cfg.blocks);
+      rc = launch_all_reduce_double_ring(dtype, ctx_, a, cfg);
+      break;
+    }
+    case ALGO_TREE: {
+      set_scratch(ensure(scratch_, tree_scratch_bytes(n, es, nnodes), "tree"));
+      int gpn = world_ / nnodes;
+      rc = launch_all_reduce_tree(dtype, ctx_, a, cfg_for(ceil_div(V, gpn), t, stream, 96, gpn));
+      break;
+    }
+    case ALGO_NVLS:
+    case ALGO_NVLS_ONESHOT: {
+      const bool oneshot = algo == ALGO_NVLS_ONESHOT;
+      const size_t bytes = V * 16;
+      // the switch reads the heap: stage tensors that live elsewhere
+      bool in_heap = a[0].in_heap_off != kNotInHeap && t.symmetric_in;
+      size_t out_off = heap_offset_of(out[0], 0);
+      bool out_heap = out_off != kNotInHeap && t.symmetric_out;
+      if (!in_heap) {
+        ensure(stage_in_, bytes, "NVLS input staging");
+        ckrt(cudaMemcpyAsync(local_ptr(stage_in_.off), in[0], n * es, cudaMemcpyDeviceToDevice,
+                             stream), "stage in");
+        a[0].in_heap_off = stage_in_.off;
+      }
+      if (!oneshot) {
+        if (!out_heap) {
+          ensure(stage_out_, bytes, "NVLS output staging");
+          a[0].out_heap_off = stage_out_.off;
+        } else {
+          a[0].out_heap_off = out_off;
+        }
+      }
+      rc = launch_all_reduce_nvls(dtype, oneshot, ctx_, a,
+                                  cfg_for(oneshot ? V : ceil_div(V, world_), t, stream, 64, 1));
+      if (rc == cudaSuccess && !oneshot && !out_heap)
+        ckrt(cudaMemcpyAsync(out[0], local_ptr(stage_out_.off), n * es, cudaMemcpyDeviceToDevice,
+                             stream), "stage out");
+      break;
+    }
+    default:
+      throw std::runtime_error("penny: unknown all-reduce algorithm " + std::to_string(algo));
+  }
+  ckrt(rc, algo_name(algo));
+}
+
+void Communicator::reduce_scatter(int dtype, const void* const* in, void* const* out,
+                                  size_t n_total, bool nvls, const Tuning& t,
+                                  cudaStream_t stream) {
+  const int es = dtype_size(dtype);
+  if (n_total == 0) return;
+  if (n_total % world_ != 0)
+    throw std::runtime_error("penny: reduce_scatter needs a multiple of the world size");
+  if (world_ == 1) {
+    if (in[0] != out[0])
+      ckrt(cudaMemcpyAsync(out[0], in[0], n_total * es, cudaMemcpyDeviceToDevice, stream), "memcpy");
+    return;
+  }
+  const size_t shard = n_total / world_;
+  const int nv = views();
+  CollArgs a[kMaxRanks];
+  memset(a, 0, sizeof(a));
+  for (int v = 0; v < nv; ++v) {
+    a[v].in = in[v];
+    a[v].out = out[v];
+    a[v].n = n_total;
+    a[v].in_heap_off = heap_offset_of(in[v], v);
+    a[v].out_heap_off = kNotInHeap;
+    a[v].nnodes = 1;
+    a[v].routes = 1;
+  }
+  const size_t SV = vecs_for(shard, es);
+  if (nvls) {
+    if (!has_multicast()) throw std::runtime_error("penny: NVLS reduce-scatter without multicast");
+    if ((shard * es) % 16 != 0) throw std::runtime_error("penny: NVLS shards must be 16-byte multiples");
+    if (a[0].in_heap_off == kNotInHeap || !t.symmetric_in) {
+      ensure(stage_in_, n_total * es, "NVLS input staging");
+      ckrt(cudaMemcpyAsync(local_ptr(stage_in_.off), in[0], n_total * es, cudaMemcpyDeviceToDevice,
+                           stream), "stage in");
+      a[0].in_heap_off = stage_in_.off;
+    }
+    ckrt(launch_reduce_scatter_nvls(dtype, ctx_, a, cfg_for(SV, t, stream, 64, 1)), "nvls rs");
+    return;
+  }
+  Region& r = ensure(scratch_, reduce_scatter_scratch_bytes(n_total, es, world_), "reduce-scatter");
+  for (int v = 0; v < nv; ++v) {
+    a[v].scratch_off = r.off;
+    a[v].scratch_bytes = r.bytes;
+  }
+  ckrt(launch_reduce_scatter(dtype, ctx_, a, cfg_for(SV, t, stream, 128, 1)), "reduce_scatter");
+}
+
+void Communicator::all_gather(int dtype, const void* const* in, void* const* out, size_t n_shard,
+                              bool nvls, const Tuning& t, cudaStream_t stream) {
+  const int es = dtype_size(dtype);
+  if (n_shard == 0) return;
+  if (world_ == 1) {
+    if (in[0] != out[0])
+      ckrt(cudaMemcpyAsync(out[0], in[0], n_shard * es, cudaMemcpyDeviceToDevice, stream), "memcpy");
+    return;
+  }
+  const int nv = views();
+  CollArgs a[kMaxRanks];
+  memset(a, 0, sizeof(a));
+  size_t oo = heap_offset_of(out[0], 0);
+  bool same = oo != kNotInHeap && (n_shard * es) % 16 == 0;
+  for (int v = 1; v < nv; ++v) same = same && heap_offset_of(out[v], v) == oo;
+  for (int v = 0; v < nv; ++v) {
+    a[v].in = in[v];
+    a[v].out = out[v];
+    a[v].n = n_shard;
+    a[v].in_heap_off = heap_offset_of(in[v], v);
+    a[v].out_heap_off = (same && t.symmetric_out) ? oo : kNotInHeap;
+    a[v].nnodes = 1;
+    a[v].routes = 1;
+  }
+  const size_t SV = vecs_for(n_shard, es);
+  if (nvls) {
+    if (!has_multicast()) throw std::runtime_error("penny: NVLS all-gather without multicast");
+    if (!same || !t.symmetric_out)
+      throw std::runtime_error(
+          "penny: NVLS all-gather needs a 16-byte-multiple shard and a symmetric output in the heap");
+    a[0].out_heap_off = oo;
+    ckrt(launch_all_gather_nvls(dtype, ctx_, a, cfg_for(SV, t, stream, 64, 1)), "nvls ag");
+    return;
+  }
+  if (a[0].out_heap_off == kNotInHeap) {
+    Region& r = ensure(scratch_, all_gather_scratch_bytes(n_shard, es, world_), "all-gather");
+    for (int v = 0; v < nv; ++v) {
+      a[v].scratch_off = r.off;
+      a[v].scratch_bytes = r.bytes;
+    }
+  }
+  ckrt(launch_all_gather(dtype, ctx_, a, cfg_for(SV, t, stream, 128, 1)), "all_gather");
+}
+
+void Communicator::all_to_all(int dtype, const void* const* in, void* const* out, size_t n_chunk,
+                              const Tuning& t, cudaStream_t stream) {
+  const int es = dtype_size(dtype);
+  if (n_chunk == 0) return;
+  if (world_ == 1) {
+    if (in[0] != out[0])
+      ckrt(cudaMemcpyAsync(out[0], in[0], n_chunk * es, cudaMemcpyDeviceToDevice, stream), "memcpy");
+    return;
+  }
+  const int nv = views();
+  CollArgs a[kMaxRanks];
+  memset(a, 0, sizeof(a));
+  size_t oo = heap_offset_of(out[0], 0);
+  bool same = oo != kNotInHeap && (n_chunk * es) % 16 == 0;
+  for (int v = 1; v < nv; ++v) same = same && heap_offset_of(out[v], v) == oo;
+  for (int v = 0; v < nv; ++v) {
+    a[v].in = in[v];
+    a[v].out = out[v];
+    a[v].n = n_chunk;
+    a[v].in_heap_off = heap_offset_of(in[v], v);
+    a[v].out_heap_off = (same && t.symmetric_out) ? oo : kNotInHeap;
+    a[v].nnodes = 1;
+    a[v].routes = 1;
+  }
+  if (a[0].out_heap_off == kNotInHeap) {
+    Region& r = ensure(scratch_, all_to_all_scratch_bytes(n_chunk, es, world_), "all-to-all");
+    for (int v = 0; v < nv; ++v) {
+      a[v].scratch_off = r.off;
+      a[v].scratch_bytes = r.bytes;
+    }
+  }
+  ckrt(launch_all_to_all(dtype, ctx_, a, cfg_for(vecs_for(n_chunk, es), t, stream, 128, 1)),
+       "all_to_all");
+}
+
+void Communicator::exchange(int dtype, void* const* buf, size_t n, const int* peers,
+                            const Tuning& t, cudaStream_t stream) {
+  const int es = dtype_size(dtype);
+  if (n == 0 || world_ == 1) return;
+  const int nv = views();
+  Region& r = ensure(scratch_pair_, exchange_scratch_bytes(n, es), "exchange");
+  CollArgs a[kMaxRanks];
+  memset(a, 0, sizeof(a));
+  for (int v = 0; v < nv; ++v) {
+    if (peers[v] < 0 || peers[v] >= world_) throw std::runtime_error("penny: bad exchange peer");
+    a[v].in = buf[v];
+    a[v].out = buf[v];
+    a[v].n = n;
+    a[v].scratch_off = r.off;
+    a[v].scratch_bytes = r.bytes;
+    a[v].in_heap_off = kNotInHeap;
+    a[v].out_heap_off = kNotInHeap;
+    a[v].peer = peers[v];
+    a[v].nnodes = 1;
+    a[v].routes = 1;
+  }
+  ckrt(launch_exchange(dtype, ctx_, a, cfg_for(vecs_for(n, es), t, stream, 128, 1)), "exchange");
+}
+
+void Communicator::fused_ar_rmsnorm(int dtype, int proto, const void* const* in,
+                                    const void* const* residual, const void* weight,
+                                    void* const* out, void* const* residual_out, int rows,
+                                    int hidden, float eps, const Tuning& t, cudaStream_t stream) {
+  const int es = dtype_size(dtype);
+  const int nv = views();
+  FusedNormArgs a[kMaxRanks];
+  memset(a, 0, sizeof(a));
+  for (int v = 0; v < nv; ++v) {
+    a[v].in = in[v];
+    a[v].residual = residual ? residual[v] : nullptr;
+    a[v].weight = weight;
+    a[v].out = out[v];
+    a[v].residual_out = residual_out ? residual_out[v] : nullptr;
+    a[v].rows = rows;
+    a[v].hidden = hidden;
+    a[v].eps = eps;
+    a[v].in_heap_off = heap_offset_of(in[v], v);
+    a[v].out_heap_off = heap_offset_of(out[v], v);
+  }
+  int threads = t.threads > 0 ? t.threads : std::min(512, std::max(32, (hidden * es / 16 + 31) / 32 * 32));
+  if (world_ == 1) {
+    ckrt(launch_add_rmsnorm(dtype, a[0], std::min(rows, 1024), threads, stream), "add_rmsnorm");
+    return;
+  }
+  LaunchCfg cfg;
+  cfg.threads = threads;
+  cfg.stream = stream;
+  cfg.emu_world = emu_ ? world_ : 0;
+  int max_blocks = emu_ ? std::max(1, 128 / world_) : 256;
+  if (proto == FUSED_PROTO_NVLS) {
+    if (!has_multicast()) throw std::runtime_error("penny: NVLS fused norm without multicast");
+    if (a[0].in_heap_off == kNotInHeap || a[0].out_heap_off == kNotInHeap || !t.symmetric_in ||
+        !t.symmetric_out)
+      throw std::runtime_error("penny: NVLS fused norm needs symmetric heap tensors for in and out");
+    cfg.blocks = t.blocks > 0 ? t.blocks : std::min(max_blocks, std::max(1, (rows + world_ - 1) / world_));
+  } else {
+    Region& r = ensure(proto == FUSED_PROTO_LL ? scratch_ll_ : scratch_,
+                       fused_norm_scratch_bytes(proto, rows, hidden, es, world_), "fused norm");
+    for (int v = 0; v < nv; ++v) {
+      a[v].scratch_off = r.off;
+      a[v].scratch_bytes = r.bytes;
+    }
+    cfg.blocks = t.blocks > 0 ? t.blocks : std::min(max_blocks, rows);
+  }
+  ckrt(launch_fused_ar_rmsnorm(dtype, proto, ctx_, a, cfg), "fused_ar_rmsnorm");
+}
+
+void Communicator::wait_selftest(cudaStream_t stream) {
+  LaunchCfg cfg;
+  cfg.blocks = 1;
+  cfg.threads = 32;
+  cfg.stream = stream;
+  cfg.emu_world = emu_ ? world_ : 0;
+  ckrt(launch_wait_selftest(ctx_, cfg), "wait_selftest");
+}
+
+StatusRecord Communicator::read_status(int view, bool clear) {
+  uint32_t w[kStatusWords];
+  char* p = heap_->base(emu_ ? view : rank_) + kStatusOffset;
+  ckrt(cudaDeviceSynchronize(), "synchronize");
+  ckrt(cudaMemcpy(w, p, sizeof(w), cudaMemcpyDeviceToHost), "read status");
+  if (clear && w[0] != 0) ckrt(cudaMemset(p, 0, sizeof(w)), "clear status");
+  StatusRecord s;
+  s.code = w[0];
+  s.rank = w[1];
+  s.peer = w[2];
+  s.block = w[3];
+  s.want = (unsigned long long)w[4] | ((unsigned long long)w[5] << 32);
+  s.seen = (unsigned long long)w[6] | ((unsigned long long)w[7] << 32);
+  return s;
+}
+
+void Communicator::host_barrier() {
+  if (bs_) bs_->barrier();
+}
+
+}  // namespace penny

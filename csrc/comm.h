@@ -1,0 +1,127 @@
+// Communicator: owns the bootstrap, the symmetric heap, the scratch regions and
+// the launch policy of every collective.  Torch-free; torch_interface.cpp wraps
+// it for Python.
+//
+// It is what the reference spreads over its `AllReduce` base class (symmetric
+// scratch + signals + epoch, csrc/common.h:21-59), the per-algorithm subclasses
+// (csrc/all_reduce_*.cu constructors) and the NVSHMEM runtime.
+//
+// Threading / ordering contract: collectives of one communicator are issued
+// from one thread onto one stream at a time, in the same order on every rank
+// (heap allocations too – they are bump-allocated, so offsets agree).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "algos.h"
+#include "bootstrap.h"
+#include "coll_args.h"
+#include "fused_ops.h"
+#include "symm_heap.h"
+
+namespace penny {
+
+struct CommOptions {
+  size_t heap_bytes = (size_t)1 << 30;
+  int heap_mode = HEAP_AUTO;
+  bool multicast = true;
+  int timeout_ms = 10000;       // bound of every device-side wait
+  int bootstrap_timeout_ms = 120000;
+};
+
+struct Tuning {
+  int blocks = 0;   // 0 = choose from the message size
+  int threads = 0;  // 0 = 512
+  int nnodes = 1;   // virtual nodes (double ring / tree / node-aware ring)
+  int routes = 0;   // 0 = choose
+  // The caller vouches that the tensor sits at the same heap offset on every
+  // rank (allocated by the same alloc() call), so peers / the switch may address
+  // it directly instead of going through scratch or staging.
+  bool symmetric_in = false;
+  bool symmetric_out = false;
+};
+
+struct StatusRecord {
+  uint32_t code, rank, peer, block;
+  unsigned long long want, seen;
+};
+
+class Communicator {
+ public:
+  // Real: one process per GPU.  uid from make_unique_id() on one rank.
+  Communicator(const std::string& uid, int rank, int world, const CommOptions& opt);
+  // Emulated: `world` virtual ranks on the current GPU of this process.
+  Communicator(int emu_world, const CommOptions& opt);
+  ~Communicator();
+
+  int rank() const { return rank_; }
+  int world() const { return world_; }
+  bool emulated() const { return emu_; }
+  int views() const { return emu_ ? world_ : 1; }  // tensors per call
+  bool has_multicast() const { return heap_->has_multicast(); }
+  std::string describe() const;
+  const CommCtx& ctx() const { return ctx_; }
+  SymmHeap& heap() { return *heap_; }
+  Bootstrap* bootstrap() { return bs_.get(); }
+
+  // Symmetric allocation (256-byte aligned); returns the heap offset.
+  size_t alloc(size_t bytes);
+  void* local_ptr(size_t off, int view = 0) const;
+  size_t heap_offset_of(const void* p, int view = 0) const;  // kNotInHeap if outside
+  size_t heap_free_bytes() const { return heap_->bytes() - arena_top_; }
+
+  // in / out: views() pointers each.  n as documented in CollArgs.
+  void all_reduce(int algo, int dtype, const void* const* in, void* const* out, size_t n,
+                  const Tuning& t, cudaStream_t stream);
+  void reduce_scatter(int dtype, const void* const* in, void* const* out, size_t n_total, bool nvls,
+                      const Tuning& t, cudaStream_t stream);
+  void all_gather(int dtype, const void* const* in, void* const* out, size_t n_shard, bool nvls,
+                  const Tuning& t, cudaStream_t stream);
+  void all_to_all(int dtype, const void* const* in, void* const* out, size_t n_chunk,
+                  const Tuning& t, cudaStream_t stream);
+  void exchange(int dtype, void* const* buf, size_t n, const int* peers, const Tuning& t,
+                cudaStream_t stream);
+  // proto: FusedProto.  Pointer arrays have views() entries.
+  void fused_ar_rmsnorm(int dtype, int proto, const void* const* in, const void* const* residual,
+                        const void* weight, void* const* out, void* const* residual_out, int rows,
+                        int hidden, float eps, const Tuning& t, cudaStream_t stream);
+
+  // Largest n an all-reduce algorithm can take in one launch with the scratch
+  // the heap can still provide (the host splits larger messages).
+  int pick_algo(int dtype, size_t n) const;
+
+  // Provokes a device-side timeout on a private flag (nothing else is touched).
+  void wait_selftest(cudaStream_t stream);
+  // Reads (and optionally clears) the status words; synchronises the device.
+  StatusRecord read_status(int view, bool clear);
+  void host_barrier();
+  void set_timeout_ms(int ms);
+  void destroy();
+
+ private:
+  struct Region {
+    size_t off = 0, bytes = 0;
+  };
+  Region& ensure(Region& r, size_t need, const char* what);
+  void init_ctx(const CommOptions& opt);
+  LaunchCfg cfg_for(size_t vecs, const Tuning& t, cudaStream_t s, int max_blocks, int multiple) const;
+  void run_all_reduce_once(int algo, int dtype, const void* const* in, void* const* out, size_t n,
+                           const Tuning& t, cudaStream_t stream);
+
+  std::unique_ptr<Bootstrap> bs_;
+  std::unique_ptr<SymmHeap> heap_;
+  CommCtx ctx_;
+  int rank_ = 0, world_ = 1;
+  bool emu_ = false;
+  size_t arena_top_ = kHeapReserved;
+  Region scratch_;       // halved, shared by the all-dependent collectives
+  Region scratch_ll_;    // halved, LL lines only
+  Region scratch_pair_;  // exchange slot
+  Region stage_in_, stage_out_;  // NVLS staging for tensors outside the heap
+  bool destroyed_ = false;
+};
+
+}  // namespace penny

@@ -1,0 +1,131 @@
+// Exchange: pairwise buffer swap and the N-way all-to-all built on the same
+// push + flag step.
+//
+//   ExchangePair – every rank swaps its buffer, in place, with rank a.peer
+//     (the peer must name this rank back).  Same contract as the reference's
+//     penny_cpp.exchange (csrc/exchange.cu:11-64), but the receive slot is
+//     persistent heap scratch: no allocation, no host barrier and no stream
+//     synchronise per call.
+//   AllToAll – out[s*n .. (s+1)*n) on rank r = in[r*n .. (r+1)*n) of rank s.
+//     The reference has no N-way form; this is what expert-parallel dispatch
+//     and combine need.
+#pragma once
+#include "coll_args.h"
+
+namespace penny {
+
+// one receive slot of [V] (not halved: see ExchangePair)
+PK_HD size_t exchange_scratch_bytes(size_t n, int elem_size) {
+  return vecs_for(n, elem_size) * 16;
+}
+// both halves of: [world][chunk vecs]
+PK_HD size_t all_to_all_scratch_bytes(size_t chunk_n, int elem_size, int world) {
+  return 2 * (size_t)world * vecs_for(chunk_n, elem_size) * 16;
+}
+
+template <typename T>
+struct ExchangePair {
+  // Not every rank depends on every other rank here, so the two-halves rule of
+  // the other collectives does not protect the slot, and exchange calls are
+  // counted on their own sequence (SEQ_PAIR).  Every rank must take part in
+  // every exchange call (with peer == its own rank to sit one out).  The pair
+  // first shakes hands ("I am in exchange call seq": my previous exchange,
+  // whoever it was with, has completely finished), then pushes, flags, copies.
+  static PK_DEV void body(const CommCtx& c, int rank, const CollArgs& a, const Blk& b, u64 seq,
+                          int& s_abort) {
+    constexpr size_t E = 16 / sizeof(T);
+    T* buf = reinterpret_cast<T*>(a.out);
+    const int peer = a.peer;
+    const size_t V = ceil_div(a.n, E);
+    const size_t stride = (size_t)b.nblocks * b.nthreads;
+    const size_t first = (size_t)b.bid * b.nthreads;
+    if (peer == rank) return;
+    PK_FOR_THREADS(b, tid) {
+      if (tid == 0) signal_peer(c, rank, peer, CH_USER, b, flag_value(seq, 1));
+    }
+    PK_FOR_THREADS(b, tid) {
+      if (tid == 0 && !wait_peer(c, rank, peer, CH_USER, b, flag_value(seq, 1), ST_TIMEOUT_DATA))
+        s_abort = 1;
+    }
+    PK_SYNC(b);
+    if (s_abort) return;
+    PK_FOR_THREADS(b, tid) {
+      for (size_t v = first + tid; v < V; v += stride)
+        st16(c.heap[peer] + a.scratch_off + v * 16, load_user_vec<T>(buf, v, a.n));
+    }
+    PK_SYNC(b);
+    PK_FOR_THREADS(b, tid) {
+      if (tid == 0) signal_peer(c, rank, peer, CH_USER, b, flag_value(seq, 2));
+    }
+    PK_FOR_THREADS(b, tid) {
+      if (tid == 0 && !wait_peer(c, rank, peer, CH_USER, b, flag_value(seq, 2), ST_TIMEOUT_DATA))
+        s_abort = 1;
+    }
+    PK_SYNC(b);
+    if (s_abort) return;
+    PK_FOR_THREADS(b, tid) {
+      for (size_t v = first + tid; v < V; v += stride)
+        store_user_vec<T>(buf, v, a.n, ld16(c.heap[rank] + a.scratch_off + v * 16));
+    }
+  }
+  static PK_DEV void run(const CommCtx& c, int rank, const CollArgs& a, const Blk& b) {
+    run_collective<ExchangePair<T>, CollArgs, SEQ_PAIR>(c, rank, a, b);
+  }
+};
+
+template <typename T, int NG>
+struct AllToAll {
+  static PK_DEV void body(const CommCtx& c, int rank, const CollArgs& a, const Blk& b, u64 seq,
+                          int& s_abort) {
+    constexpr size_t E = 16 / sizeof(T);
+    const T* in = reinterpret_cast<const T*>(a.in);
+    T* out = reinterpret_cast<T*>(a.out);
+    const size_t CV = ceil_div(a.n, E);
+    const bool direct = a.out_heap_off != kNotInHeap;
+    const size_t stride = (size_t)b.nblocks * b.nthreads;
+    const size_t first = (size_t)b.bid * b.nthreads;
+    if (direct) {
+      // the peers' outputs are written in place: wait until every peer is in this call
+      PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 1), s_abort);
+      if (s_abort) return;
+      PK_FOR_THREADS(b, tid) {
+        for (int d = 0; d < NG; ++d) {
+          const int p = (rank + d) % NG;
+          T* dst = reinterpret_cast<T*>(c.heap[p] + a.out_heap_off) + (size_t)rank * a.n;
+          for (size_t j = first + tid; j < CV; j += stride)
+            store_user_vec<T>(dst, j, a.n, load_user_vec<T>(in + (size_t)p * a.n, j, a.n));
+        }
+      }
+      PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 2), s_abort);
+      return;
+    }
+    const size_t base = scratch_half(a.scratch_off, a.scratch_bytes, seq);
+    PK_FOR_THREADS(b, tid) {
+      for (int d = 0; d < NG; ++d) {
+        const int p = (rank + d) % NG;
+        for (size_t j = first + tid; j < CV; j += stride) {
+          V16 x = load_user_vec<T>(in + (size_t)p * a.n, j, a.n);
+          if (p == rank)
+            store_user_vec<T>(out + (size_t)rank * a.n, j, a.n, x);
+          else
+            st16(c.heap[p] + base + ((size_t)rank * CV + j) * 16, x);
+        }
+      }
+    }
+    PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 1), s_abort);
+    if (s_abort) return;
+    PK_FOR_THREADS(b, tid) {
+      for (int d = 1; d < NG; ++d) {
+        const int s = (rank + d) % NG;
+        for (size_t j = first + tid; j < CV; j += stride)
+          store_user_vec<T>(out + (size_t)s * a.n, j, a.n,
+                            ld16(c.heap[rank] + base + ((size_t)s * CV + j) * 16));
+      }
+    }
+  }
+  static PK_DEV void run(const CommCtx& c, int rank, const CollArgs& a, const Blk& b) {
+    run_collective<AllToAll<T, NG>, CollArgs>(c, rank, a, b);
+  }
+};
+
+}  // namespace penny

@@ -1,0 +1,324 @@
+// All-reduce fused with its tensor-parallel consumer: residual add + RMSNorm.
+//
+// In a TP transformer layer the row-parallel GEMMs (o_proj, down_proj) leave a
+// partial sum [rows, hidden] on every rank; what the next op needs is
+//     z   = sum_over_ranks(partial) + residual          (new residual stream)
+//     out = z * rsqrt(mean(z^2) + eps) * weight         (input of the next GEMM)
+// Done separately that is an all-reduce, a write of the sum, and a second kernel
+// that re-reads it.  Here the rows never leave registers between the reduction
+// and the normalisation, and there is one launch instead of two or three.
+//
+// Three transports, all one block per row:
+//   LL    every rank pushes its partial rows to every peer as flag-in-data
+//         lines and polls for the peers' lines: no barrier, lowest latency, 2x
+//         wire bytes.  Best for a handful of rows.
+//   FLAG  16-byte pushes + one flag barrier per block.
+//   NVLS  rows are sharded over the ranks; the owner pulls the switch-reduced
+//         row (multimem.ld_reduce), normalises it and multicasts the result
+//         (multimem.st).  The residual stream stays sharded: each rank only
+//         keeps the residual of the rows it owns.  Least wire traffic.
+// Plus the communication-free kernel (add_rmsnorm) used at world size 1.
+//
+// The reference stops at the plain all-reduce (penny/custom_all_reduce.py:229-267);
+// the norm runs as a separate kernel of the serving framework.
+#include "algos.h"
+#include "all_reduce_oneshot.cuh"
+#include "fused_ops.h"
+#include "launch.cuh"
+#include "schedule.h"
+
+namespace penny {
+
+constexpr int kMaxVecPerThread = 4;
+
+__device__ __forceinline__ float block_sum(float v, float* smem) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  __syncthreads();  // smem may still be read from the previous row
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? smem[lane] : 0.f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return t;
+}
+
+// z (fp32, K vectors per thread) -> residual_out / out for one row.
+template <typename T, int K>
+__device__ __forceinline__ void norm_and_store(float (&z)[K][16 / sizeof(T)], int nv, int HV,
+                                               const FusedNormArgs& a, size_t row, float* smem) {
+  constexpr int E = 16 / sizeof(T);
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    if (k < nv) {
+#pragma unroll
+      for (int i = 0; i < E; ++i) ss += z[k][i] * z[k][i];
+    }
+  }
+  ss = block_sum(ss, smem);
+  const float rstd = rsqrtf(ss / (float)a.hidden + a.eps);
+  T* out = reinterpret_cast<T*>(a.out) + row * (size_t)a.hidden;
+  T* rout = a.residual_out ? reinterpret_cast<T*>(a.residual_out) + row * (size_t)a.hidden : nullptr;
+  const T* w = reinterpret_cast<const T*>(a.weight);
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    if (k < nv) {
+      const int v = threadIdx.x + k * blockDim.x;
+      if (rout) st16(rout + (size_t)v * E, pack<T>(z[k]));
+      float wv[E], o[E];
+      unpack_set<T>(ld16(w + (size_t)v * E), wv);
+#pragma unroll
+      for (int i = 0; i < E; ++i) o[i] = z[k][i] * rstd * wv[i];
+      st16(out + (size_t)v * E, pack<T>(o));
+    }
+  }
+  (void)HV;
+}
+
+// ---------------------------------------------------------------------------
+// communication-free: out = rmsnorm(in + residual)
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(512) k_add_rmsnorm(const FusedNormArgs a) {
+  constexpr int E = 16 / sizeof(T);
+  __shared__ float smem[32];
+  const int HV = a.hidden / E;
+  for (size_t row = blockIdx.x; row < (size_t)a.rows; row += gridDim.x) {
+    float z[kMaxVecPerThread][E];
+    int nv = 0;
+#pragma unroll
+    for (int k = 0; k < kMaxVecPerThread; ++k) {
+      const int v = threadIdx.x + k * blockDim.x;
+      if (v < HV) {
+        nv = k + 1;
+        unpack_set<T>(ld16(reinterpret_cast<const T*>(a.in) + row * a.hidden + (size_t)v * E), z[k]);
+        if (a.residual)
+          unpack_add<T>(ld16(reinterpret_cast<const T*>(a.residual) + row * a.hidden + (size_t)v * E),
+                        z[k]);
+      }
+    }
+    norm_and_store<T, kMaxVecPerThread>(z, nv, HV, a, row, smem);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// one-shot (LL or flag) + residual + RMSNorm
+// scratch half: LL   [src][rows][HV] pairs of lines
+//               FLAG [src][rows][HV] vectors
+// ---------------------------------------------------------------------------
+template <typename T, int NG, bool LL>
+struct FusedOneShotNorm {
+  static __device__ void body(const CommCtx& c, int rank, const FusedNormArgs& a, const Blk& b,
+                              u64 seq, int& s_abort) {
+    constexpr int E = 16 / sizeof(T);
+    __shared__ float smem[32];
+    const int HV = a.hidden / E;
+    const size_t base = scratch_half(a.scratch_off, a.scratch_bytes, seq);
+    const uint32_t e = ll_flag(seq);
+    const T* in = reinterpret_cast<const T*>(a.in);
+    constexpr size_t LINE = LL ? 32 : 16;
+
+    // push my partial rows to every peer
+    for (size_t row = b.bid; row < (size_t)a.rows; row += b.nblocks) {
+      for (int v = threadIdx.x; v < HV; v += blockDim.x) {
+        const V16 x = ld16(in + row * a.hidden + (size_t)v * E);
+        const size_t off = base + (((size_t)rank * a.rows + row) * HV + v) * LINE;
+        if (LL) {
+          V16 l0, l1;
+          l0.w[0] = x.w[0]; l0.w[1] = e; l0.w[2] = x.w[1]; l0.w[3] = e;
+          l1.w[0] = x.w[2]; l1.w[1] = e; l1.w[2] = x.w[3]; l1.w[3] = e;
+#pragma unroll
+          for (int d = 1; d < NG; ++d) {
+            char* dst = c.heap[(rank + d) % NG] + off;
+            st16_volatile(dst, l0);
+            st16_volatile(dst + 16, l1);
+          }
+        } else {
+#pragma unroll
+          for (int d = 1; d < NG; ++d) st16(c.heap[(rank + d) % NG] + off, x);
+        }
+      }
+    }
+    if (!LL) {
+      PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 1), s_abort);
+      if (s_abort) return;
+    }
+    // reduce in rank order, add the residual, normalise
+    for (size_t row = b.bid; row < (size_t)a.rows; row += b.nblocks) {
+      float z[kMaxVecPerThread][E];
+      int nv = 0;
+      bool ok = true;
+#pragma unroll
+      for (int k = 0; k < kMaxVecPerThread; ++k) {
+        const int v = threadIdx.x + k * blockDim.x;
+        if (v < HV) {
+          nv = k + 1;
+#pragma unroll
+          for (int i = 0; i < E; ++i) z[k][i] = 0.f;
+#pragma unroll
+          for (int s = 0; s < NG; ++s) {
+            V16 x;
+            if (s == rank) {
+              x = ld16(in + row * a.hidden + (size_t)v * E);
+            } else {
+              const char* src = c.heap[rank] + base + (((size_t)s * a.rows + row) * HV + v) * LINE;
+              if (LL) {
+                V16 l0, l1;
+                ok = ok && ll_wait_line(src, e, l0, c, s, b.bid);
+                ok = ok && ll_wait_line(src + 16, e, l1, c, s, b.bid);
+                x.w[0] = l0.w[0]; x.w[1] = l0.w[2]; x.w[2] = l1.w[0]; x.w[3] = l1.w[2];
+              } else {
+                x = ld16(src);
+              }
+            }
+            unpack_add<T>(x, z[k]);
+          }
+          if (a.residual)
+            unpack_add<T>(
+                ld16(reinterpret_cast<const T*>(a.residual) + row * a.hidden + (size_t)v * E), z[k]);
+        }
+      }
+      if (LL) {
+        // a timeout anywhere in the block abandons the row for the whole block
+        if (__syncthreads_or(ok ? 0 : 1)) return;
+      }
+      norm_and_store<T, kMaxVecPerThread>(z, nv, HV, a, row, smem);
+    }
+  }
+  static __device__ void run(const CommCtx& c, int rank, const FusedNormArgs& a, const Blk& b) {
+    run_collective<FusedOneShotNorm<T, NG, LL>, FusedNormArgs>(c, rank, a, b);
+  }
+};
+
+// ---------------------------------------------------------------------------
+// NVLS: rows sharded over ranks; owner reduces in the switch, normalises,
+// multicasts.  in / out live in the heap; residual(_out) hold this rank's rows
+// only, indexed by global row (so the buffers are [rows, hidden] everywhere but
+// only the owned rows are meaningful).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ V16 mm_ld_reduce_bf16(const void* p) {
+  V16 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3])
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ V16 mm_ld_reduce_f16(const void* p) {
+  V16 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3])
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ V16 mm_ld_reduce_f32(const void* p) {
+  V16 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3])
+               : "l"(p)
+               : "memory");
+  return v;
+}
+template <typename T>
+__device__ __forceinline__ V16 mm_ld_reduce(const void* p) {
+  if constexpr (sizeof(T) == 4) return mm_ld_reduce_f32(p);
+  else if constexpr (std::is_same<T, __half>::value) return mm_ld_reduce_f16(p);
+  else return mm_ld_reduce_bf16(p);
+}
+__device__ __forceinline__ void mm_st(void* p, const V16& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p),
+               "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3])
+               : "memory");
+}
+
+template <typename T>
+struct FusedNvlsNorm {
+  static __device__ void body(const CommCtx& c, int rank, const FusedNormArgs& a, const Blk& b,
+                              u64 seq, int& s_abort) {
+    constexpr int E = 16 / sizeof(T);
+    __shared__ float smem[32];
+    const int HV = a.hidden / E;
+    const Span mine = split_span((size_t)a.rows, c.world, rank);
+    const T* w = reinterpret_cast<const T*>(a.weight);
+    PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 1), s_abort);
+    if (s_abort) return;
+    for (size_t row = mine.begin + b.bid; row < mine.end; row += b.nblocks) {
+      float z[kMaxVecPerThread][E];
+      int nv = 0;
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < kMaxVecPerThread; ++k) {
+        const int v = threadIdx.x + k * blockDim.x;
+        if (v < HV) {
+          nv = k + 1;
+          const size_t eoff = (row * a.hidden + (size_t)v * E) * sizeof(T);
+          unpack_set<T>(mm_ld_reduce<T>(c.mc + a.in_heap_off + eoff), z[k]);
+          if (a.residual)
+            unpack_add<T>(
+                ld16(reinterpret_cast<const T*>(a.residual) + row * a.hidden + (size_t)v * E), z[k]);
+#pragma unroll
+          for (int i = 0; i < E; ++i) ss += z[k][i] * z[k][i];
+        }
+      }
+      ss = block_sum(ss, smem);
+      const float rstd = rsqrtf(ss / (float)a.hidden + a.eps);
+      T* rout =
+          a.residual_out ? reinterpret_cast<T*>(a.residual_out) + row * (size_t)a.hidden : nullptr;
+#pragma unroll
+      for (int k = 0; k < kMaxVecPerThread; ++k) {
+        if (k < nv) {
+          const int v = threadIdx.x + k * blockDim.x;
+          if (rout) st16(rout + (size_t)v * E, pack<T>(z[k]));
+          float wv[E], o[E];
+          unpack_set<T>(ld16(w + (size_t)v * E), wv);
+#pragma unroll
+          for (int i = 0; i < E; ++i) o[i] = z[k][i] * rstd * wv[i];
+          const size_t eoff = (row * a.hidden + (size_t)v * E) * sizeof(T);
+          mm_st(c.mc + a.out_heap_off + eoff, pack<T>(o));
+        }
+      }
+    }
+    PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 2), s_abort);
+  }
+  static __device__ void run(const CommCtx& c, int rank, const FusedNormArgs& a, const Blk& b) {
+    run_collective<FusedNvlsNorm<T>, FusedNormArgs>(c, rank, a, b);
+  }
+};
+
+static bool shape_ok(int dtype, const FusedNormArgs& a, int threads) {
+  const int E = 16 / dtype_size(dtype);
+  if (a.hidden % E != 0) return false;
+  return a.hidden / E <= kMaxVecPerThread * threads && a.rows >= 1;
+}
+
+cudaError_t launch_add_rmsnorm(int dtype, const FusedNormArgs& a, int blocks, int threads,
+                               cudaStream_t stream) {
+  if (!shape_ok(dtype, a, threads)) return cudaErrorInvalidValue;
+  PENNY_DISPATCH_DTYPE(dtype, T, (k_add_rmsnorm<T><<<blocks, threads, 0, stream>>>(a)));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fused_ar_rmsnorm(int dtype, int proto, const CommCtx& c, const FusedNormArgs* a,
+                                    const LaunchCfg& cfg) {
+  if (!shape_ok(dtype, a[0], cfg.threads)) return cudaErrorInvalidValue;
+  cudaError_t rc = cudaErrorInvalidValue;
+  if (proto == FUSED_PROTO_NVLS) {
+    if (c.mc == nullptr || cfg.emu_world > 0 || a[0].in_heap_off == kNotInHeap ||
+        a[0].out_heap_off == kNotInHeap)
+      return cudaErrorNotSupported;
+    PENNY_DISPATCH_DTYPE(dtype, T, rc = (launch_body<FusedNvlsNorm<T>, FusedNormArgs>(c, a, cfg)));
+    return rc;
+  }
+  PENNY_DISPATCH_DTYPE(dtype, T, PENNY_DISPATCH_WORLD(c.world, NG, return cudaErrorInvalidValue, {
+    rc = (proto == FUSED_PROTO_LL)
+             ? launch_body<FusedOneShotNorm<T, NG, true>, FusedNormArgs>(c, a, cfg)
+             : launch_body<FusedOneShotNorm<T, NG, false>, FusedNormArgs>(c, a, cfg);
+  }));
+  return rc;
+}
+
+}  // namespace penny

@@ -1,0 +1,234 @@
+"""Communicator: the Python face of the symmetric heap and its collectives.
+
+Two kinds, one API:
+
+* ``Communicator.create(group)`` – one process per GPU.  Rank 0 of ``group``
+  (any torch.distributed group; gloo is enough) draws a unique id, the id is
+  broadcast as an object, and every rank joins the native bootstrap (Unix
+  sockets + fd passing) that builds the peer-mapped heap and, when the driver
+  allows it, the NVLS multicast mapping.  torch.distributed is not used again.
+* ``Communicator.emulated(world)`` – all ranks on ONE GPU, every collective one
+  cooperative launch.  Arguments are then lists with one tensor per virtual
+  rank.  This is how the multi-rank kernels are tested on a single GPU.
+
+The reference reaches the same point with ``initialize_distributed`` + NVSHMEM
+(penny/utils.py:39-52) and per-algorithm objects (csrc/common.h:89-118).
+"""
+from __future__ import annotations
+
+import os
+from typing import List, Optional, Sequence, Union
+
+import torch
+
+from .._ext import ops
+
+TensorOrList = Union[torch.Tensor, Sequence[torch.Tensor]]
+
+ALGOS = {
+    "auto": ops.ALGO_AUTO,
+    "ring_standard": ops.ALGO_RING_STANDARD,
+    "ring": ops.ALGO_RING_STANDARD,
+    "ring_simple": ops.ALGO_RING_SIMPLE,
+    "oneshot": ops.ALGO_ONESHOT,
+    "twoshot": ops.ALGO_TWOSHOT,
+    "double_ring": ops.ALGO_DOUBLE_RING,
+    "tree": ops.ALGO_TREE,
+    "nvls": ops.ALGO_NVLS,
+    "oneshot_ll": ops.ALGO_ONESHOT_LL,
+    "nvls_oneshot": ops.ALGO_NVLS_ONESHOT,
+}
+ALGO_NAMES = {v: k for k, v in ALGOS.items() if k not in ("ring",)}
+PROTOS = {"ll": ops.PROTO_LL, "flag": ops.PROTO_FLAG, "nvls": ops.PROTO_NVLS}
+
+STATUS_NAMES = {
+    0: "ok", 1: "timeout in a barrier", 2: "timeout waiting for data", 3: "timeout waiting for a credit",
+    4: "timeout waiting for a low-latency line", 5: "timeout waiting for a tile", 6: "self test",
+    7: "bad arguments",
+}
+
+
+class PennyTimeoutError(RuntimeError):
+    """A device-side wait ran out; ``record`` says who waited for whom."""
+
+    def __init__(self, record: dict):
+        self.record = record
+        super().__init__(
+            f"penny: {STATUS_NAMES.get(record['code'], record['code'])}: rank {record['rank']} "
+            f"block {record['block']} waited for rank {record['peer']} "
+            f"(want {record['want']}, saw {record['seen']})")
+
+
+def _algo_id(algo) -> int:
+    if isinstance(algo, str):
+        if algo not in ALGOS:
+            raise ValueError(f"unknown algorithm {algo!r}; one of {sorted(ALGOS)}")
+        return ALGOS[algo]
+    return int(algo)
+
+
+class Communicator:
+    def __init__(self, handle: int, emulated: bool):
+        self._h = handle
+        self.emulated = emulated
+        self.rank = ops.comm_rank(handle)
+        self.world_size = ops.comm_world(handle)
+        self.views = ops.comm_views(handle)
+        # data_ptr of tensors handed out by empty(): symmetric by construction
+        self._symmetric = {}
+
+    # ------------------------------------------------------------------ creation
+    @classmethod
+    def create(cls, group=None, heap_bytes: Optional[int] = None, multicast: bool = True,
+               heap_mode: str = "auto", timeout_ms: int = 0) -> "Communicator":
+        import torch.distributed as dist
+
+        rank = dist.get_rank(group)
+        world = dist.get_world_size(group)
+        box = [bytes(ops.get_unique_id()) if rank == 0 else None]
+        src = dist.get_global_rank(group, 0) if group is not None else 0
+        dist.broadcast_object_list(box, src=src, group=group, device="cpu")
+        mode = {"auto": 0, "vmm": 1, "ipc": 2}[heap_mode]
+        if heap_bytes is None:
+            heap_bytes = int(os.environ.get("PENNY_HEAP_BYTES", 1 << 30))
+        h = ops.comm_create(box[0], rank, world, int(heap_bytes), mode, multicast, int(timeout_ms))
+        return cls(h, emulated=False)
+
+    @classmethod
+    def emulated(cls, world: int, heap_bytes: int = 256 << 20, timeout_ms: int = 2000) -> "Communicator":
+        return cls(ops.comm_create_emulated(world, int(heap_bytes), int(timeout_ms)), emulated=True)
+
+    def close(self):
+        if self._h:
+            ops.comm_destroy(self._h)
+            self._h = 0
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ------------------------------------------------------------------- queries
+    @property
+    def has_multicast(self) -> bool:
+        return ops.comm_has_multicast(self._h)
+
+    def describe(self) -> str:
+        return ops.comm_describe(self._h)
+
+    def heap_free(self) -> int:
+        return ops.comm_heap_free(self._h)
+
+    def barrier(self):
+        """Host-side barrier over the native bootstrap (no-op when emulated)."""
+        ops.comm_barrier(self._h)
+
+    def set_timeout_ms(self, ms: int):
+        ops.comm_set_timeout_ms(self._h, int(ms))
+
+    def pick_algo(self, dtype: torch.dtype, numel: int) -> str:
+        dt = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[dtype]
+        return ALGO_NAMES[ops.comm_pick_algo(self._h, dt, int(numel))]
+
+    # ------------------------------------------------------------------ tensors
+    def empty(self, *shape, dtype=torch.bfloat16):
+        """A tensor in the symmetric heap: same offset on every rank, so peers
+        (and the NVSwitch) can address it directly.  Every rank must call this in
+        the same order.  Emulated: a list with one tensor per virtual rank."""
+        if len(shape) == 1 and isinstance(shape[0], (tuple, list, torch.Size)):
+            shape = tuple(shape[0])
+        ts = ops.comm_empty(self._h, list(shape), dtype)
+        for t in ts:
+            self._symmetric[t.data_ptr()] = t.numel() * t.element_size()
+        return list(ts) if self.emulated else ts[0]
+
+    def is_symmetric(self, t: TensorOrList) -> bool:
+        ts = self._as_list(t)
+        return all(x.data_ptr() in self._symmetric for x in ts)
+
+    def _as_list(self, t: TensorOrList) -> List[torch.Tensor]:
+        if isinstance(t, torch.Tensor):
+            ts = [t]
+        else:
+            ts = list(t)
+        if len(ts) != self.views:
+            raise ValueError(f"expected {self.views} tensor(s), got {len(ts)}")
+        return ts
+
+    def _ret(self, ts: List[torch.Tensor]):
+        return ts if self.emulated else ts[0]
+
+    # -------------------------------------------------------------- collectives
+    def all_reduce(self, inp: TensorOrList, out: Optional[TensorOrList] = None, algo="auto",
+                   blocks: int = 0, threads: int = 0, nnodes: int = 1, routes: int = 0):
+        ins = self._as_list(inp)
+        outs = self._as_list(out) if out is not None else [torch.empty_like(x) for x in ins]
+        ops.comm_all_reduce(self._h, ins, outs, _algo_id(algo), blocks, threads, nnodes, routes,
+                            self.is_symmetric(ins), self.is_symmetric(outs))
+        return self._ret(outs)
+
+    def reduce_scatter(self, inp: TensorOrList, out: Optional[TensorOrList] = None, nvls: bool = False,
+                       blocks: int = 0, threads: int = 0):
+        ins = self._as_list(inp)
+        if out is None:
+            outs = [torch.empty(x.numel() // self.world_size, dtype=x.dtype, device=x.device) for x in ins]
+        else:
+            outs = self._as_list(out)
+        ops.comm_reduce_scatter(self._h, ins, outs, nvls, blocks, threads, self.is_symmetric(ins))
+        return self._ret(outs)
+
+    def all_gather(self, inp: TensorOrList, out: Optional[TensorOrList] = None, nvls: bool = False,
+                   blocks: int = 0, threads: int = 0):
+        ins = self._as_list(inp)
+        if out is None:
+            outs = [torch.empty(x.numel() * self.world_size, dtype=x.dtype, device=x.device) for x in ins]
+        else:
+            outs = self._as_list(out)
+        ops.comm_all_gather(self._h, ins, outs, nvls, blocks, threads, self.is_symmetric(outs))
+        return self._ret(outs)
+
+    def all_to_all(self, inp: TensorOrList, out: Optional[TensorOrList] = None, blocks: int = 0,
+                   threads: int = 0):
+        ins = self._as_list(inp)
+        outs = self._as_list(out) if out is not None else [torch.empty_like(x) for x in ins]
+        ops.comm_all_to_all(self._h, ins, outs, blocks, threads, self.is_symmetric(outs))
+        return self._ret(outs)
+
+    def exchange(self, buf: TensorOrList, peer: Union[int, Sequence[int]], blocks: int = 0, threads: int = 0):
+        """In-place pairwise swap.  Every rank must call it; a rank that sits a
+        round out passes its own rank as ``peer``."""
+        bufs = self._as_list(buf)
+        peers = [int(peer)] if isinstance(peer, int) else [int(p) for p in peer]
+        ops.comm_exchange(self._h, bufs, peers, blocks, threads)
+        return self._ret(bufs)
+
+    def fused_all_reduce_rmsnorm(self, inp: TensorOrList, weight: torch.Tensor, residual: Optional[TensorOrList] = None,
+                                 out: Optional[TensorOrList] = None, residual_out: Optional[TensorOrList] = None,
+                                 eps: float = 1e-5, proto: str = "ll", blocks: int = 0, threads: int = 0):
+        """out = rmsnorm(all_reduce(inp) + residual) * weight; residual_out = all_reduce(inp) + residual."""
+        ins = self._as_list(inp)
+        outs = self._as_list(out) if out is not None else [torch.empty_like(x) for x in ins]
+        res = self._as_list(residual) if residual is not None else []
+        if residual_out is not None:
+            rout = self._as_list(residual_out)
+        else:
+            rout = res  # in place on the residual stream
+        sym = self.is_symmetric(ins) and self.is_symmetric(outs)
+        ops.comm_fused_ar_rmsnorm(self._h, ins, res, weight, outs, rout, float(eps), PROTOS[proto],
+                                  blocks, threads, sym)
+        return self._ret(outs), (self._ret(rout) if rout else None)
+
+    # ------------------------------------------------------------------- status
+    def status(self, view: int = 0, clear: bool = True) -> dict:
+        return dict(ops.comm_status(self._h, view, clear))
+
+    def check(self):
+        """Synchronise and raise PennyTimeoutError if any device-side wait ran out."""
+        recs = [self.status(v, clear=True) for v in range(self.views)]
+        for rec in recs:
+            if rec["code"] != 0:
+                raise PennyTimeoutError(rec)
+
+    def wait_selftest(self):
+        ops.comm_wait_selftest(self._h)
