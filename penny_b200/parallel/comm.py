@@ -68,8 +68,9 @@ def _algo_id(algo) -> int:
 
 
 class Communicator:
-    def __init__(self, handle: int, emulated: bool):
+    def __init__(self, handle: int, emulated: bool, owned: bool = True):
         self._h = handle
+        self._owned = owned  # False: the extension's global communicator (penny_cpp.finalize frees it)
         self.emulated = emulated
         self.rank = ops.comm_rank(handle)
         self.world_size = ops.comm_world(handle)
@@ -100,7 +101,8 @@ class Communicator:
 
     def close(self):
         if self._h:
-            ops.comm_destroy(self._h)
+            if self._owned:
+                ops.comm_destroy(self._h)
             self._h = 0
 
     def __del__(self):

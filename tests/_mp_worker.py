@@ -1,0 +1,254 @@
+"""Worker of the multi-process GPU tests: one process per GPU, launched by
+torch.distributed.run.  Writes a JSON report that the test reads."""
+import json
+import os
+import sys
+import traceback
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+TOL = {torch.float32: dict(atol=1e-5, rtol=1e-5), torch.bfloat16: dict(atol=6e-2, rtol=2e-2),
+       torch.float16: dict(atol=1e-2, rtol=1e-2)}
+
+
+def gather_cpu(t):
+    """All ranks' tensors on the CPU (through gloo), as the oracle's input."""
+    parts = [torch.empty(t.shape, dtype=t.dtype) for _ in range(dist.get_world_size())]
+    dist.all_gather(parts, t.cpu())
+    return parts
+
+
+def main():
+    out_path = sys.argv[1]
+    use_nvls = os.environ.get("PENNY_TEST_NVLS", "1") == "1"
+    from penny_b200.utils import initialize_distributed, shutdown
+    rank, world, _ = initialize_distributed(init_native=False)
+    from penny_b200.parallel.comm import Communicator
+    report = {"world": world, "failures": [], "checked": 0}
+    comm = Communicator.create(None, heap_bytes=1 << 30, multicast=use_nvls, timeout_ms=5000)
+    report["describe"] = comm.describe()
+    report["multicast"] = comm.has_multicast
+
+    def check(name, fn):
+        try:
+            fn()
+            report["checked"] += 1
+        except Exception as e:  # noqa: BLE001
+            report["failures"].append(f"{name}: {type(e).__name__}: {str(e)[:300]}")
+            traceback.print_exc()
+
+    algos = ["oneshot", "oneshot_ll", "twoshot", "ring_simple", "ring_standard", "double_ring", "tree"]
+    if comm.has_multicast:
+        algos += ["nvls", "nvls_oneshot"]
+
+    for dtype in (torch.float32, torch.bfloat16):
+        for n in (1, 1023, 4096, 65536, 1 << 20):
+            g = torch.Generator(device="cuda").manual_seed(1234 + rank + n)
+            x = (torch.rand(n, device="cuda", generator=g) * 2 - 1).to(dtype)
+            parts = gather_cpu(x)
+            want = torch.stack([p.float() for p in parts]).sum(0)
+            for algo in algos:
+                nnodes = 2 if algo in ("double_ring", "tree") and world >= 4 else 1
+
+                def run(algo=algo, nnodes=nnodes):
+                    out = comm.all_reduce(x, algo=algo, nnodes=nnodes)
+                    comm.check()
+                    torch.testing.assert_close(out.float().cpu(), want, **TOL[dtype])
+                    outs = gather_cpu(out)
+                    for o in outs[1:]:
+                        assert torch.equal(o, outs[0]), "ranks disagree bitwise"
+                check(f"all_reduce/{algo}/{dtype}/{n}", run)
+
+            if comm.has_multicast and (n * x.element_size()) % 16 == 0:
+                def run_sym():
+                    xs = comm.empty(n, dtype=dtype)
+                    xs.copy_(x)
+                    ys = comm.empty(n, dtype=dtype)
+                    comm.all_reduce(xs, out=ys, algo="nvls")
+                    comm.check()
+                    torch.testing.assert_close(ys.float().cpu(), want, **TOL[dtype])
+                    comm.all_reduce(xs, out=xs, algo="nvls")  # in place
+                    comm.check()
+                    torch.testing.assert_close(xs.float().cpu(), want, **TOL[dtype])
+                check(f"all_reduce/nvls-symmetric/{dtype}/{n}", run_sym)
+
+            shard = n
+            big = (torch.rand(shard * world, device="cuda", generator=g) * 2 - 1).to(dtype)
+            bparts = gather_cpu(big)
+            bsum = torch.stack([p.float() for p in bparts]).sum(0)
+
+            def run_rs(nvls=False):
+                o = comm.reduce_scatter(big, nvls=nvls)
+                comm.check()
+                torch.testing.assert_close(o.float().cpu(), bsum[rank * shard:(rank + 1) * shard], **TOL[dtype])
+            check(f"reduce_scatter/{dtype}/{n}", run_rs)
+            if comm.has_multicast and (shard * x.element_size()) % 16 == 0:
+                check(f"reduce_scatter/nvls/{dtype}/{n}", lambda: run_rs(True))
+
+            def run_ag():
+                o = comm.all_gather(x)
+                comm.check()
+                assert torch.equal(o.cpu(), torch.cat(parts))
+            check(f"all_gather/{dtype}/{n}", run_ag)
+            if comm.has_multicast and (shard * x.element_size()) % 16 == 0:
+                def run_ag_nvls():
+                    o = comm.empty(shard * world, dtype=dtype)
+                    comm.all_gather(x, out=o, nvls=True)
+                    comm.check()
+                    assert torch.equal(o.cpu(), torch.cat(parts))
+                check(f"all_gather/nvls/{dtype}/{n}", run_ag_nvls)
+
+            def run_a2a():
+                o = comm.all_to_all(big)
+                comm.check()
+                want_r = torch.cat([bparts[s][rank * shard:(rank + 1) * shard] for s in range(world)])
+                assert torch.equal(o.cpu(), want_r)
+            check(f"all_to_all/{dtype}/{n}", run_a2a)
+
+            def run_ex():
+                b = x.clone()
+                comm.exchange(b, rank ^ 1)
+                comm.check()
+                assert torch.equal(b.cpu(), parts[rank ^ 1])
+            check(f"exchange/{dtype}/{n}", run_ex)
+
+    # fused all-reduce + residual + RMSNorm
+    hidden = 4096
+    protos = ["ll", "flag"] + (["nvls"] if comm.has_multicast else [])
+    for rows in (1, 8, 64, 256):
+        g = torch.Generator(device="cuda").manual_seed(77 + rank + rows)
+        xin = (torch.randn(rows, hidden, device="cuda", generator=g) * 0.5).bfloat16()
+        g2 = torch.Generator(device="cuda").manual_seed(5)
+        res = torch.randn(rows, hidden, device="cuda", generator=g2).bfloat16()
+        w = (torch.rand(hidden, device="cuda", generator=g2) + 0.5).bfloat16()
+        parts = gather_cpu(xin)
+        z = torch.stack([p.float() for p in parts]).sum(0) + res.float().cpu()
+        want = z * torch.rsqrt(z.pow(2).mean(-1, keepdim=True) + 1e-5) * w.float().cpu()
+        for proto in protos:
+            def run_fused(proto=proto):
+                if proto == "nvls":
+                    xi = comm.empty(rows, hidden, dtype=torch.bfloat16)
+                    xi.copy_(xin)
+                    out = comm.empty(rows, hidden, dtype=torch.bfloat16)
+                else:
+                    xi, out = xin, torch.empty_like(xin)
+                r = res.clone()
+                comm.fused_all_reduce_rmsnorm(xi, w, residual=r, out=out, proto=proto)
+                comm.check()
+                torch.testing.assert_close(out.float().cpu(), want, **TOL[torch.bfloat16])
+                if proto == "nvls":  # residual stream stays sharded by row
+                    lo = (rows + world - 1) // world * rank
+                    hi = min(rows, lo + (rows + world - 1) // world)
+                    if hi > lo:
+                        torch.testing.assert_close(r[lo:hi].float().cpu(), z[lo:hi], **TOL[torch.bfloat16])
+                else:
+                    torch.testing.assert_close(r.float().cpu(), z, **TOL[torch.bfloat16])
+            check(f"fused_norm/{proto}/{rows}", run_fused)
+
+    # CUDA graph replay of the device-side call counter
+    def run_graph():
+        x = torch.ones(8192, device="cuda", dtype=torch.bfloat16) * (rank + 1)
+        y = torch.empty_like(x)
+        comm.all_reduce(x, out=y, algo="oneshot_ll")
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            comm.all_reduce(x, out=y, algo="oneshot_ll")
+            comm.all_reduce(y, out=y, algo="twoshot")
+        for _ in range(5):
+            gr.replay()
+        comm.check()
+        s = world * (world + 1) / 2
+        assert torch.allclose(y.float(), torch.full_like(y, s * world).float()), y[:4]
+    check("cuda_graph_replay", run_graph)
+
+    # ---- the reference-style module API on the process-wide communicator ----
+    import penny_cpp
+    from penny_b200.utils import global_communicator
+    gcomm = global_communicator(heap_bytes=256 << 20)
+
+    def run_handle_api():
+        n = 1 << 18
+        buf = torch.full((n,), float(rank + 1), device="cuda", dtype=torch.float16)
+        out = torch.empty_like(buf)
+        for algo in (0, 1, 2, 3, 4, 5):
+            h = penny_cpp.all_reduce_create(buf, 16, 256, 2 if algo in (4, 5) and world >= 4 else 1, 1, algo)
+            penny_cpp.all_reduce_run(h, out)
+            penny_cpp.all_reduce_run(h, out)
+            penny_cpp.all_reduce_destroy(h)
+            gcomm.check()
+            assert torch.all(out == world * (world + 1) / 2), (algo, out[:4])
+        b = torch.full((n,), float(rank), device="cuda", dtype=torch.float16)
+        penny_cpp.nvshmem_register(b)
+        penny_cpp.exchange(b, 512, 1024, rank ^ 1)
+        penny_cpp.nvshmem_unregister(b)
+        gcomm.check()
+        assert torch.all(b == float(rank ^ 1))
+    check("reference_module_api", run_handle_api)
+
+    # ---- drop-in CustomAllreduce: eager, registered, CUDA-graph capture ----
+    from penny.custom_all_reduce import CustomAllreduce
+    gloo = dist.new_group(backend="gloo")
+    car = CustomAllreduce(gloo, torch.cuda.current_device())
+
+    def run_custom():
+        assert not car.disabled
+        for dtype in (torch.float32, torch.float16, torch.bfloat16):
+            for n in (8, 4096, 1 << 18, (1 << 20) + 64):
+                g = torch.Generator(device="cuda").manual_seed(99 + rank + n)
+                x = (torch.rand(n, device="cuda", generator=g) * 2 - 1).to(dtype)
+                parts = gather_cpu(x)
+                want = torch.stack([p.float() for p in parts]).sum(0)
+                if not car.should_custom_ar(x):
+                    continue
+                y = car.custom_all_reduce(x)
+                assert car.status()[0] == 0
+                torch.testing.assert_close(y.float().cpu(), want, **TOL[dtype])
+                if n % world == 0 and (n // world * x.element_size()) % 16 == 0:
+                    rs = car.custom_reduce_scatter(x)
+                    sh = n // world
+                    torch.testing.assert_close(rs[:sh].float().cpu(), want[rank * sh:(rank + 1) * sh], **TOL[dtype])
+                if n * world * x.element_size() < car.max_size:
+                    ag = car.custom_all_gather(x)
+                    assert torch.equal(ag.cpu(), torch.cat(parts))
+        assert car.custom_all_reduce(torch.ones(3, device="cuda")) is None  # 12 bytes: not a multiple of 16
+    check("custom_all_reduce_eager", run_custom)
+
+    def run_custom_graph():
+        x = torch.full((4096,), float(rank + 1), device="cuda", dtype=torch.bfloat16)
+        with car.capture():
+            car.custom_all_reduce(x)  # warm-up: allocation only
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                y = car.custom_all_reduce(x)
+                z = car.custom_all_reduce(y)
+        for _ in range(3):
+            gr.replay()
+        torch.cuda.synchronize()
+        assert car.status()[0] == 0
+        s = world * (world + 1) / 2
+        assert torch.all(y.float() == s) and torch.all(z.float() == s * world)
+    check("custom_all_reduce_graph", run_custom_graph)
+    car.close()
+
+    torch.cuda.synchronize()
+    dist.barrier()
+    all_reports = [None] * world
+    dist.all_gather_object(all_reports, report)
+    comm.close()
+    if rank == 0:
+        merged = {"world": world, "multicast": report["multicast"], "describe": report["describe"],
+                  "checked": sum(r["checked"] for r in all_reports),
+                  "failures": [f"rank{i}: {f}" for i, r in enumerate(all_reports) for f in r["failures"]]}
+        with open(out_path, "w") as f:
+            json.dump(merged, f, indent=1)
+    shutdown()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,88 @@
+"""Schedule properties, enumerated on the CPU from the same header the kernels use."""
+import itertools
+
+import pytest
+
+from penny_b200.parallel import schedule
+
+
+@pytest.mark.parametrize("world", [2, 3, 4, 6, 8])
+def test_stride_rings_are_hamiltonian(world):
+    seen = set()
+    for route in range(8):
+        order = schedule.ring_order(world, 1, route)
+        assert sorted(order) == list(range(world))
+        seen.add(tuple(order))
+    if world == 8:
+        assert len(seen) == 4  # strides 1, 7, 3, 5
+
+
+@pytest.mark.parametrize("world,nnodes", [(8, 2), (8, 4), (4, 2), (6, 2), (6, 3)])
+def test_node_aware_rings(world, nnodes):
+    gpn = world // nnodes
+    for route in range(2 * max(1, gpn // 2)):
+        order = schedule.ring_order(world, nnodes, route)
+        assert sorted(order) == list(range(world))
+        # a ring crosses each node boundary exactly once per lap
+        crossings = sum(1 for i in range(world) if order[i] // gpn != order[(i + 1) % world] // gpn)
+        assert crossings == nnodes
+    # odd routes are the even ring walked backwards
+    fwd, bwd = schedule.ring_order(world, nnodes, 0), schedule.ring_order(world, nnodes, 1)
+    assert bwd == [fwd[(world - p) % world] for p in range(world)]
+    if gpn >= 4:
+        # different ring pairs leave a node from different local ranks
+        exit0 = [fwd[i] % gpn for i in range(world) if fwd[i] // gpn != fwd[(i + 1) % world] // gpn]
+        o2 = schedule.ring_order(world, nnodes, 2)
+        exit2 = [o2[i] % gpn for i in range(world) if o2[i] // gpn != o2[(i + 1) % world] // gpn]
+        assert set(exit0).isdisjoint(exit2)
+
+
+@pytest.mark.parametrize("n", [2, 3, 4, 6, 8])
+def test_ring_steps_pair_up_and_cover(n):
+    """What position p sends at step s is what p+1 receives at step s, every chunk
+    is reduced exactly n-1 times and every rank ends with every chunk."""
+    have = [{c: {p} for c in range(n)} for p in range(n)]  # contributions folded into chunk c at position p
+    complete = [set() for _ in range(n)]
+    for step in range(2 * (n - 1)):
+        sends = {}
+        for p in range(n):
+            sc, rc, reduce = schedule.ring_step_chunks(n, p, step)
+            sends[p] = (sc, reduce)
+        for p in range(n):
+            sc, rc, reduce = schedule.ring_step_chunks(n, p, step)
+            prev = (p - 1) % n
+            assert sends[prev][0] == rc, "receive schedule must match the predecessor's send schedule"
+        new = [dict(h) for h in have]
+        for p in range(n):
+            _, rc, reduce = schedule.ring_step_chunks(n, p, step)
+            prev = (p - 1) % n
+            incoming = have[prev][rc]
+            if reduce:
+                assert have[p][rc].isdisjoint(incoming), "a contribution was added twice"
+                new[p][rc] = have[p][rc] | incoming
+            else:
+                assert incoming == set(range(n)), "all-gather forwarded an unfinished chunk"
+                new[p][rc] = incoming
+        have = new
+    for p in range(n):
+        for c in range(n):
+            assert have[p][c] == set(range(n))
+
+
+@pytest.mark.parametrize("gpn", [1, 2, 4, 8])
+def test_tree_chains(gpn):
+    for tree in range(gpn):
+        chain = schedule.tree_chain(gpn, tree)
+        assert sorted(chain) == list(range(gpn))
+        assert chain[-1] == tree  # root
+    if gpn >= 4:
+        # odd trees walk the node the other way round
+        assert schedule.tree_chain(gpn, 0)[0] != schedule.tree_chain(gpn, 1)[0] or gpn == 2
+
+
+def test_split_span_partitions():
+    for total, parts in itertools.product([0, 1, 7, 64, 1000, 4097], [1, 2, 3, 8]):
+        spans = [schedule.split_span(total, parts, i) for i in range(parts)]
+        assert spans[0][0] == 0 and spans[-1][1] == total
+        for (b0, e0), (b1, e1) in zip(spans, spans[1:]):
+            assert e0 == b1 and b0 <= e0
