@@ -1,0 +1,72 @@
+// Torch-facing wrappers of the decode-step kernels.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <pybind11/pybind11.h>
+#include <torch/extension.h>
+
+#include "decode_kernels.h"
+
+namespace py = pybind11;
+using namespace penny;
+
+namespace {
+cudaStream_t cur() { return at::cuda::getCurrentCUDAStream().stream(); }
+void need(bool ok, const char* msg) { TORCH_CHECK(ok, "penny: ", msg); }
+void ck(cudaError_t rc, const char* what) {
+  TORCH_CHECK(rc == cudaSuccess, "penny: ", what, ": ", cudaGetErrorString(rc));
+}
+bool bf16_cuda(const at::Tensor& t) {
+  return t.is_cuda() && t.is_contiguous() && t.scalar_type() == at::kBFloat16;
+}
+}  // namespace
+
+void bind_decode(py::module_& m) {
+  m.def("rope_append", [](at::Tensor qkv, at::Tensor kcache, at::Tensor vcache, at::Tensor positions,
+                          int64_t Hq, int64_t Hkv, int64_t D, double theta) {
+    need(bf16_cuda(qkv) && bf16_cuda(kcache) && bf16_cuda(vcache), "rope_append expects contiguous bf16 CUDA tensors");
+    need(positions.is_cuda() && positions.scalar_type() == at::kInt && positions.is_contiguous(), "positions must be int32 CUDA");
+    need(qkv.dim() == 2 && qkv.size(1) == (Hq + 2 * Hkv) * D, "qkv must be [B, (Hq + 2 Hkv) D]");
+    need(kcache.dim() == 4 && kcache.size(0) == qkv.size(0) && kcache.size(1) == Hkv && kcache.size(3) == D &&
+             vcache.sizes() == kcache.sizes(), "caches must be [B, Hkv, max_len, D]");
+    need(positions.numel() == qkv.size(0), "one position per row");
+    const at::cuda::OptionalCUDAGuard guard(qkv.device());
+    ck(launch_rope_append(qkv.data_ptr(), kcache.data_ptr(), vcache.data_ptr(), positions.data_ptr<int>(),
+                          (int)qkv.size(0), (int)Hq, (int)Hkv, (int)D, (int)kcache.size(2), (float)theta, cur()),
+       "rope_append");
+  });
+  m.def("decode_attn_workspace_bytes", [](int64_t B, int64_t Hq, int64_t splits) {
+    return (int64_t)decode_attn_workspace_bytes((int)B, (int)Hq, (int)splits);
+  });
+  m.def("decode_attention", [](at::Tensor qkv, at::Tensor kcache, at::Tensor vcache, at::Tensor positions,
+                               at::Tensor out, at::Tensor workspace, int64_t Hq, int64_t Hkv, int64_t splits,
+                               double scale) {
+    need(bf16_cuda(qkv) && bf16_cuda(kcache) && bf16_cuda(vcache) && bf16_cuda(out), "decode_attention expects contiguous bf16 CUDA tensors");
+    need(positions.is_cuda() && positions.scalar_type() == at::kInt, "positions must be int32 CUDA");
+    const int64_t B = qkv.size(0), D = kcache.size(3);
+    need(qkv.size(1) == (Hq + 2 * Hkv) * D && out.numel() == B * Hq * D, "decode_attention shapes");
+    need(workspace.is_cuda() && (int64_t)workspace.nbytes() >= (int64_t)decode_attn_workspace_bytes((int)B, (int)Hq, (int)splits),
+         "workspace too small (decode_attn_workspace_bytes)");
+    need(((uintptr_t)workspace.data_ptr() & 15) == 0, "workspace must be 16-byte aligned");
+    const at::cuda::OptionalCUDAGuard guard(qkv.device());
+    ck(launch_decode_attention(qkv.data_ptr(), kcache.data_ptr(), vcache.data_ptr(), positions.data_ptr<int>(),
+                               out.data_ptr(), workspace.data_ptr(), (int)B, (int)Hq, (int)Hkv, (int)D,
+                               (int)kcache.size(2), (int)splits, (float)scale, cur()),
+       "decode_attention");
+  });
+  m.def("silu_mul", [](at::Tensor gate_up, at::Tensor out) {
+    need(bf16_cuda(gate_up) && bf16_cuda(out) && gate_up.dim() == 2, "silu_mul expects [rows, 2F] bf16");
+    const int64_t rows = gate_up.size(0), F = gate_up.size(1) / 2;
+    need(out.numel() == rows * F, "silu_mul output must be [rows, F]");
+    const at::cuda::OptionalCUDAGuard guard(gate_up.device());
+    ck(launch_silu_mul(gate_up.data_ptr(), out.data_ptr(), (int)rows, (int)F, cur()), "silu_mul");
+  });
+  m.def("argmax_rows", [](at::Tensor logits, at::Tensor out_val, at::Tensor out_idx, int64_t index_base) {
+    need(bf16_cuda(logits) && logits.dim() == 2, "argmax_rows expects [rows, cols] bf16");
+    need(out_val.is_cuda() && out_val.scalar_type() == at::kFloat && out_val.numel() == logits.size(0), "out_val [rows] fp32");
+    need(out_idx.is_cuda() && out_idx.scalar_type() == at::kLong && out_idx.numel() == logits.size(0), "out_idx [rows] int64");
+    const at::cuda::OptionalCUDAGuard guard(logits.device());
+    ck(launch_argmax(logits.data_ptr(), (int)logits.size(0), (int)logits.size(1), out_val.data_ptr<float>(),
+                     (long long*)out_idx.data_ptr<int64_t>(), (long long)index_base, cur()),
+       "argmax_rows");
+  });
+}

@@ -1,0 +1,31 @@
+// Entry points of the decode-step kernels (csrc/decode_kernels.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+namespace penny {
+
+// qkv: [B, (Hq + 2*Hkv) * D] bf16; caches: [B, Hkv, max_len, D] bf16; positions: [B] int32.
+// Rotates q and k in place (rotate-half RoPE) and stores the new k, v rows at positions[b].
+cudaError_t launch_rope_append(void* qkv, void* kcache, void* vcache, const int* positions, int B,
+                               int Hq, int Hkv, int D, int max_len, float theta,
+                               cudaStream_t stream);
+
+// Scratch the split-KV attention needs: per (row, head, split) an unnormalised
+// fp32 output row plus (max, sum).
+size_t decode_attn_workspace_bytes(int B, int Hq, int splits);
+
+// out: [B, Hq * D] bf16.  Attends to cache rows [0, positions[b]] (inclusive).
+cudaError_t launch_decode_attention(const void* qkv, const void* kcache, const void* vcache,
+                                    const int* positions, void* out, void* workspace, int B, int Hq,
+                                    int Hkv, int D, int max_len, int splits, float scale,
+                                    cudaStream_t stream);
+
+// gate_up: [rows, 2F] (gate | up) -> out [rows, F] = silu(gate) * up
+cudaError_t launch_silu_mul(const void* gate_up, void* out, int rows, int F, cudaStream_t stream);
+
+// logits: [rows, cols] bf16 -> per-row max value and index (+ index_base)
+cudaError_t launch_argmax(const void* logits, int rows, int cols, float* out_val, long long* out_idx,
+                          long long index_base, cudaStream_t stream);
+
+}  // namespace penny

@@ -30,6 +30,7 @@ using namespace penny;
 
 void bind_custom_all_reduce(py::module_& m);  // custom_all_reduce_binding.cpp
 void bind_gemm(py::module_& m);               // gemm_binding.cpp
+void bind_decode(py::module_& m);             // decode_binding.cpp
 
 namespace {
 
@@ -409,4 +410,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 
   bind_custom_all_reduce(m);
   bind_gemm(m);
+  bind_decode(m);
 }

@@ -30,11 +30,13 @@ CUDA_SOURCES = [
     "csrc/fused_ar_rmsnorm.cu",
     "csrc/custom_all_reduce.cu",
     "csrc/comm.cu",
+    "csrc/decode_kernels.cu",
 ]
 CPP_SOURCES = [
     "csrc/torch_interface.cpp",
     "csrc/custom_all_reduce_binding.cpp",
     "csrc/gemm_binding.cpp",
+    "csrc/decode_binding.cpp",
     "csrc/bootstrap.cpp",
     "csrc/symm_heap.cpp",
 ]

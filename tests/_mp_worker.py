@@ -166,6 +166,37 @@ def main():
         assert torch.allclose(y.float(), torch.full_like(y, s * world).float()), y[:4]
     check("cuda_graph_replay", run_graph)
 
+    # ---- tensor-parallel decoder vs the same model on one GPU ----
+    def run_tp_decode():
+        from penny_b200.models.llama_tp import LlamaConfig, LlamaTPDecoder
+        cfg = LlamaConfig.tiny()
+        if cfg.kv_heads % world:
+            cfg.kv_heads, cfg.heads = world, 4 * world
+        B, kv = 4, 100
+        full = LlamaTPDecoder(cfg, world=1, max_batch=B, max_len=160, use_graph=False, full_init=True)
+        full.fill_synthetic_kv(kv)
+        protos = ["ll", "flag"] + (["nvls"] if comm.has_multicast else [])
+        for backend, proto in [("penny", p) for p in protos] + [("penny_unfused", "flag"), ("nccl", "flag")]:
+            tp = LlamaTPDecoder(cfg, comm=comm, rank=rank, world=world, max_batch=B, max_len=160,
+                                backend=backend, proto=proto, use_graph=(backend != "nccl"), full_init=True)
+            hk = cfg.kv_heads // world
+            for li in range(cfg.layers):
+                tp.kcache[li].copy_(full.kcache[li][:, rank * hk:(rank + 1) * hk])
+                tp.vcache[li].copy_(full.vcache[li][:, rank * hk:(rank + 1) * hk])
+            tp.positions.copy_(full.positions)
+            tp.tokens.copy_(full.tokens)
+            tp.capture()
+            want = full.reference_logits(full.tokens, full.positions, full.kcache, full.vcache)
+            tp.step_device()
+            comm.check()
+            got = tp.logits.float()
+            ref_shard = want[:, rank * tp.V:(rank + 1) * tp.V]
+            err = (got - ref_shard).abs().max().item()
+            assert err < 0.05 * want.std().item() + 0.02, (backend, proto, err)
+            chosen = want.gather(1, tp.next_tokens[:, None]).squeeze(1)
+            assert torch.all(chosen >= want.max(-1).values - 0.1 * want.std()), (backend, proto)
+    check("tp_decode", run_tp_decode)
+
     # ---- the reference-style module API on the process-wide communicator ----
     import penny_cpp
     from penny_b200.utils import global_communicator
