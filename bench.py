@@ -18,8 +18,9 @@ every step.
 `--impl reference` runs the unmodified reference (baseline/_ref, NVSHMEM build)
 through its own public API – `penny.utils.initialize_distributed` and
 `penny.custom_all_reduce.CustomAllreduce` (with CUDA-graph capture, NCCL when it
-declines) – under a plain-PyTorch implementation of the same model; nothing of
-this repository's package is imported on that path.
+declines) – under a plain-PyTorch implementation of the same model with fixed
+shapes, captured in a CUDA graph as the serving engines do; nothing of this
+repository's package is imported on that path.
 """
 import argparse
 import json
@@ -225,7 +226,6 @@ def run_reference(args):
     dt = torch.bfloat16
     H, D, L, B = 4096, 128, args.layers, args.batch
     Hq, Hkv, Fl, Vl = 32 // world, 8 // world, 14336 // world, 128256 // world
-    max_len = args.kv_len + args.steps * 2 + args.warmup * 2 + 64
     g = torch.Generator(device=dev).manual_seed(rank + 1)
 
     def rnd(*s):
@@ -234,11 +234,18 @@ def run_reference(args):
     ones = torch.ones(H, dtype=dt, device=dev)
     layers = [dict(wqkv=rnd((Hq + 2 * Hkv) * D, H), wo=rnd(H, Hq * D), wgu=rnd(2 * Fl, H), wdown=rnd(H, Fl))
               for _ in range(L)]
+    max_len = args.kv_len + 2 * (args.steps + args.warmup) + 8
     kc = [torch.randn(B, Hkv, max_len, D, device=dev, generator=g, dtype=torch.float32).to(dt) for _ in range(L)]
     vc = [torch.randn(B, Hkv, max_len, D, device=dev, generator=g, dtype=torch.float32).to(dt) for _ in range(L)]
     tokens = torch.randint(0, 128256, (B,), device=dev, generator=g)
     next_tokens = torch.zeros_like(tokens)
     inv = 500000.0 ** (-torch.arange(0, D // 2, device=dev, dtype=torch.float32) * 2 / D)
+    # Fixed shapes (full-length cache + additive mask, position held in a device
+    # tensor) so that the step can be captured in a CUDA graph, the way vLLM /
+    # SGLang run decode with the reference's CustomAllreduce.capture().
+    pos_t = torch.full((1,), args.kv_len, dtype=torch.int64, device=dev)
+    mask = torch.full((1, 1, 1, max_len), float("-inf"), dtype=dt, device=dev)
+    mask[..., :args.kv_len] = 0
 
     def all_reduce(x):
         if world == 1:
@@ -253,20 +260,20 @@ def run_reference(args):
         a, b = t[..., :D // 2].float(), t[..., D // 2:].float()
         return torch.cat([a * cos - b * sin, b * cos + a * sin], -1).to(dt)
 
-    def step(pos):
+    def step():
         res = embed[tokens]
         x = F.rms_norm(res, (H,), ones, 1e-5)
-        ang = float(pos) * inv
+        ang = pos_t.float() * inv
         cos, sin = ang.cos(), ang.sin()
+        mask.index_fill_(3, pos_t, 0.0)
         for li, W in enumerate(layers):
             qkv = F.linear(x, W["wqkv"])
             q = rope(qkv[:, :Hq * D].view(B, Hq, D), cos, sin)
             k = rope(qkv[:, Hq * D:(Hq + Hkv) * D].view(B, Hkv, D), cos, sin)
             v = qkv[:, (Hq + Hkv) * D:].view(B, Hkv, D)
-            kc[li][:, :, pos] = k
-            vc[li][:, :, pos] = v
-            att = F.scaled_dot_product_attention(q.unsqueeze(2), kc[li][:, :, :pos + 1], vc[li][:, :, :pos + 1],
-                                                 enable_gqa=True)
+            kc[li].index_copy_(2, pos_t, k.unsqueeze(2))
+            vc[li].index_copy_(2, pos_t, v.unsqueeze(2))
+            att = F.scaled_dot_product_attention(q.unsqueeze(2), kc[li], vc[li], attn_mask=mask, enable_gqa=True)
             o = all_reduce(F.linear(att.reshape(B, Hq * D), W["wo"]))
             res = res + o
             x = F.rms_norm(res, (H,), ones, 1e-5)
@@ -277,22 +284,52 @@ def run_reference(args):
         logits = F.linear(x, lm_head)
         val, idx = logits.float().max(dim=-1)
         if world > 1:
-            vals = [torch.empty_like(val) for _ in range(world)]
-            idxs = [torch.empty_like(idx) for _ in range(world)]
-            dist.all_gather(vals, val)
-            dist.all_gather(idxs, idx + rank * Vl)
-            best = torch.stack(vals).argmax(0, keepdim=True)
-            idx = torch.stack(idxs).gather(0, best).view(B)
+            vals = torch.empty(world, B, dtype=val.dtype, device=dev)
+            idxs = torch.empty(world, B, dtype=idx.dtype, device=dev)
+            dist.all_gather_into_tensor(vals, val)
+            dist.all_gather_into_tensor(idxs, idx + rank * Vl)
+            best = vals.argmax(0, keepdim=True)
+            idx = idxs.gather(0, best).view(B)
         next_tokens.copy_(idx)
         tokens.copy_(idx)
+        pos_t.add_(1)
 
-    # The KV length changes every step, so a single captured graph would not be the
-    # same computation; the reference path runs eagerly, as its eager public API
-    # (custom_all_reduce outside capture()) is specified to.
-    pos = args.kv_len
+    def reset():
+        pos_t.fill_(args.kv_len)
+        mask.fill_(float("-inf"))
+        mask[..., :args.kv_len] = 0
+
+    graph, mode = None, "eager"
+    try:
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            step()
+            step()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        if car is not None:
+            with car.capture():
+                with torch.cuda.graph(graph):
+                    step()
+        else:
+            with torch.cuda.graph(graph):
+                step()
+        torch.cuda.synchronize()
+        mode = "cuda graph"
+    except Exception as e:  # noqa: BLE001
+        graph, mode = None, f"eager (graph capture failed: {str(e)[:80]})"
+    reset()
+
+    def run_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            step()
+
     for _ in range(args.warmup):
-        step(pos)
-        pos += 1
+        run_step()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -303,8 +340,7 @@ def run_reference(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        step(pos)
-        pos += 1
+        run_step()
     e1.record()
     torch.cuda.synchronize()
     if world > 1:
@@ -314,12 +350,11 @@ def run_reference(args):
     # end to end: pinned host tokens in, host tokens out, every step
     host_in = torch.randint(0, 128256, (B,), dtype=torch.int64).pin_memory()
     host_out = torch.zeros(B, dtype=torch.int64).pin_memory()
-    pos = args.kv_len
+    reset()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         tokens.copy_(host_in, non_blocking=True)
-        step(pos)
-        pos += 1
+        run_step()
         host_out.copy_(next_tokens, non_blocking=True)
         torch.cuda.synchronize()
         host_in.copy_(host_out)
@@ -337,7 +372,7 @@ def run_reference(args):
             "data": "synthetic tokens + synthetic KV cache, random-init weights", "impl": "reference",
             "config": {"model": "Llama-3-8B-shaped (hidden 4096, 32 layers, 32q/8kv heads, FFN 14336, vocab 128256)"
                        if L == 32 else f"DEBUG {L} layers", "global_batch": B, "seq_len": args.kv_len,
-                       "parallelism": f"tp{world}", "allreduce": "reference CustomAllreduce (eager), NCCL fallback",
+                       "parallelism": f"tp{world}", "allreduce": "reference CustomAllreduce, NCCL fallback", "mode": mode,
                        "model_code": "plain PyTorch (the reference ships no model)",
                        "l2": "inputs larger than L2 (weights + KV streamed every step)"},
             "clocks": clocks,

@@ -19,6 +19,9 @@ namespace penny {
 namespace {
 
 __device__ __forceinline__ float bf2f(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ uint32_t smem_u32_local(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
 
 // ---------------------------------------------------------------------------
 // RoPE (rotate-half form) on q and k, then k / v written into the cache.
@@ -55,142 +58,234 @@ __global__ void k_rope_append(__nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __
 }
 
 // ---------------------------------------------------------------------------
-// Decode attention, head_dim 128, grouped queries.
+// Decode attention, head_dim 128, grouped queries, on tensor cores.
 //
-// One block per (batch row, KV head, split of the KV length).  The G = Hq / Hkv
-// query heads that share the KV head are the block's G warps, so K and V are
-// read from HBM once for all of them.  KV positions are processed in tiles of
-// 32: the tile is brought into shared memory with 16-byte cp.async (double
-// buffered), lane l owns dims [4l, 4l+4) of every row, the 32 partial dot
-// products of a tile are transposed-and-summed across the warp with 31 shuffles
-// (instead of 5 per position), and lane p ends up with the score of position p.
-// Each split writes an unnormalised output + (max, sum); k_attn_merge combines.
+// One block per (batch row, KV head, split of the KV length), 4 warps.  Each
+// warp walks its own tiles of 16 KV positions with a private 3-stage cp.async
+// pipeline (no block-wide barrier in the loop) and serves ALL G = Hq / Hkv query
+// heads of the KV head at once: the heads are the M rows (padded to 16) of
+// mma.sync m16n8k16, so K and V are read from HBM once for the whole group and
+// the inner loop is ~30 tensor-core instructions per tile instead of thousands
+// of scalar FMAs and shuffles.
+//   S = Q K^T : A = Q fragments (registers, pre-scaled by scale * log2 e),
+//               B = K rows via ldmatrix from 128-byte-XOR-swizzled shared memory
+//   O += P V  : A = P re-packed from the S accumulators, B = V via ldmatrix.trans
+// Softmax is online in the log2 domain; the four warps' (max, sum, O) are merged
+// through shared memory.  With one split the normalised bf16 output is written
+// directly, otherwise an unnormalised fp32 partial + (max, sum) that
+// k_attn_merge combines.
 // ---------------------------------------------------------------------------
 constexpr int kD = 128;
-constexpr int kTile = 32;
+constexpr int kTile = 16;          // KV positions per pipeline stage
+constexpr int kAttnWarps = 4;
+constexpr int kAttnStages = 3;
+constexpr int kStageBytes = kTile * kD * 2 * 2;  // K + V
+constexpr int kAttnSmem = kAttnWarps * kAttnStages * kStageBytes;  // 96 KB
+constexpr float kLog2e = 1.4426950408889634f;
 
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool pred) {
-  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+__device__ __forceinline__ void cp_async16(uint32_t smem, const void* gmem, bool pred) {
   const int bytes = pred ? 16 : 0;  // zero-fill when out of range
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem), "l"(gmem), "r"(bytes));
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N));
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
 }
 
 template <int G>
-__global__ void __launch_bounds__(G * 32) k_decode_attn(
+__global__ void __launch_bounds__(kAttnWarps * 32) k_decode_attn(
     const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ kcache,
     const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ positions,
-    float* __restrict__ part_o, float* __restrict__ part_ml, int Hq, int Hkv, int max_len,
-    int splits, float scale) {
-  __shared__ __align__(16) __nv_bfloat16 sk[2][kTile][kD];
-  __shared__ __align__(16) __nv_bfloat16 sv[2][kTile][kD];
+    __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+    int Hq, int Hkv, int max_len, int splits, float scale) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int b = blockIdx.x, kh = blockIdx.y, sp = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
   const int len = positions[b] + 1;  // the new token was appended at positions[b]
   const int per = ((len + splits - 1) / splits + kTile - 1) / kTile * kTile;
   const int t0 = sp * per;
   const int t1 = min(len, t0 + per);
-  const int hq = kh * G + warp;
+  const int ntiles = t1 > t0 ? (t1 - t0 + kTile - 1) / kTile : 0;
+  const uint32_t wbase = smem_u32_local(smem_raw) + warp * (kAttnStages * kStageBytes);
 
-  // this warp's query head, pre-scaled, 4 dims per lane
-  float q[4];
+  // Q fragments of this KV head's G query heads: rows g < G, 8 K-chunks of 16 dims
+  uint32_t qa[8][2];
   {
-    const __nv_bfloat16* qp = qkv + (size_t)b * (Hq + 2 * Hkv) * kD + (size_t)hq * kD + lane * 4;
-    const uint2 raw = *reinterpret_cast<const uint2*>(qp);
-    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-    const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-    q[0] = bf2f(a.x) * scale; q[1] = bf2f(a.y) * scale; q[2] = bf2f(c.x) * scale; q[3] = bf2f(c.y) * scale;
+    const float qs = scale * kLog2e;
+    const __nv_bfloat16* qp = qkv + (size_t)b * (Hq + 2 * Hkv) * kD + (size_t)(kh * G + (g < G ? g : 0)) * kD;
+#pragma unroll
+    for (int kc = 0; kc < 8; ++kc) {
+      const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(qp + kc * 16 + 2 * t);
+      const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(qp + kc * 16 + 8 + 2 * t);
+      qa[kc][0] = (g < G) ? pack2(bf2f(lo.x) * qs, bf2f(lo.y) * qs) : 0u;
+      qa[kc][1] = (g < G) ? pack2(bf2f(hi.x) * qs, bf2f(hi.y) * qs) : 0u;
+    }
   }
   const __nv_bfloat16* kbase = kcache + ((size_t)b * Hkv + kh) * (size_t)max_len * kD;
   const __nv_bfloat16* vbase = vcache + ((size_t)b * Hkv + kh) * (size_t)max_len * kD;
 
-  auto load_tile = [&](int stage, int start) {
-    // 32 rows x 256 B = 512 chunks of 16 B for K, the same for V
-    for (int c = threadIdx.x; c < kTile * 16; c += G * 32) {
-      const int r = c >> 4, o = (c & 15) * 8;
-      const bool ok = start + r < t1;
-      const size_t g = (size_t)(ok ? start + r : 0) * kD + o;
-      cp_async16(&sk[stage][r][o], kbase + g, ok);
-      cp_async16(&sv[stage][r][o], vbase + g, ok);
-    }
-    cp_async_commit();
-  };
-
-  float m = -INFINITY, l = 0.f;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  const int ntiles = t1 > t0 ? (t1 - t0 + kTile - 1) / kTile : 0;
-  if (ntiles > 0) load_tile(0, t0);
-  for (int t = 0; t < ntiles; ++t) {
-    const int stage = t & 1;
-    if (t + 1 < ntiles) {
-      load_tile(stage ^ 1, t0 + (t + 1) * kTile);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
-    // partial dot products of my 4 dims with the 32 rows of the tile
-    float p[kTile];
+  // tile j of this warp -> positions [t0 + (warp + 4 j) * 16, +16)
+  auto issue = [&](int j) {
+    const int tile = warp + kAttnWarps * j;
+    if (tile < ntiles) {
+      const int start = t0 + tile * kTile;
+      const uint32_t sb = wbase + (j % kAttnStages) * kStageBytes;
 #pragma unroll
-    for (int r = 0; r < kTile; ++r) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(&sk[stage][r][lane * 4]);
-      const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-      const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-      p[r] = q[0] * bf2f(a.x) + q[1] * bf2f(a.y) + q[2] * bf2f(c.x) + q[3] * bf2f(c.y);
-    }
-    // transpose-and-sum: afterwards lane j holds the full score of row j
-#pragma unroll
-    for (int w = 16; w >= 1; w >>= 1) {
-      const bool upper = (lane & w) != 0;
-#pragma unroll
-      for (int i = 0; i < w; ++i) {
-        // keep the half that matches my bit, send the other half
-        const float send = upper ? p[i] : p[i + w];
-        const float keep = upper ? p[i + w] : p[i];
-        p[i] = keep + __shfl_xor_sync(0xffffffffu, send, w);
+      for (int i = 0; i < 8; ++i) {
+        const int row = 2 * i + (lane >> 4), chunk = lane & 15;
+        const bool ok = start + row < t1;
+        const size_t goff = (size_t)(ok ? start + row : t0) * kD + chunk * 8;
+        const uint32_t soff = row * 256 + ((chunk ^ (row & 7)) << 4);
+        cp_async16(sb + soff, kbase + goff, ok);
+        cp_async16(sb + kTile * 256 + soff, vbase + goff, ok);
       }
     }
-    // After the last step p[0] is the score of row `lane` with bits taken MSB first:
-    // row index = lane (bit w of lane selected the upper half at every step).
-    const int row = t0 + t * kTile + lane;
-    float s = (row < t1) ? p[0] : -INFINITY;
-    float tmax = s;
+    cp_async_commit();  // always: keeps the group count in step with j
+  };
+
+  float m = -INFINITY, l = 0.f;  // row g (valid for g < G); l is this thread's share
+  float o[16][4];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
-    const float mnew = fmaxf(m, tmax);
-    const float corr = __expf(m - mnew);
-    const float e = (row < t1) ? __expf(s - mnew) : 0.f;
-    float tsum = e;
+  for (int dc = 0; dc < 16; ++dc) o[dc][0] = o[dc][1] = o[dc][2] = o[dc][3] = 0.f;
+
+  const int my_tiles = ntiles > warp ? (ntiles - warp + kAttnWarps - 1) / kAttnWarps : 0;
+  issue(0);
+  issue(1);
+  for (int j = 0; j < my_tiles; ++j) {
+    __syncwarp();  // everyone is done with the stage that tile j + 2 overwrites
+    issue(j + 2);
+    cp_async_wait<2>();
+    __syncwarp();
+    const uint32_t sb = wbase + (j % kAttnStages) * kStageBytes;
+    const int start = t0 + (warp + kAttnWarps * j) * kTile;
+    // ---- S = Q K^T: two N-chunks of 8 positions ----
+    float s[2][4];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) tsum += __shfl_xor_sync(0xffffffffu, tsum, o);
-    l = l * corr + tsum;
-    m = mnew;
+    for (int nc = 0; nc < 2; ++nc) {
+      s[nc][0] = s[nc][1] = s[nc][2] = s[nc][3] = 0.f;
+      const int row = nc * 8 + (lane & 7);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) acc[i] *= corr;
-#pragma unroll
-    for (int r = 0; r < kTile; ++r) {
-      const float pr = __shfl_sync(0xffffffffu, e, r);
-      const uint2 raw = *reinterpret_cast<const uint2*>(&sv[stage][r][lane * 4]);
-      const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-      const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-      acc[0] += pr * bf2f(a.x); acc[1] += pr * bf2f(a.y); acc[2] += pr * bf2f(c.x); acc[3] += pr * bf2f(c.y);
+      for (int kp = 0; kp < 4; ++kp) {  // pairs of K-chunks
+        const int chunk = kp * 4 + (lane >> 3);
+        uint32_t kb[4];
+        ldmatrix_x4(sb + row * 256 + ((chunk ^ (row & 7)) << 4), kb);
+        mma_bf16(s[nc], qa[2 * kp][0], 0u, qa[2 * kp][1], 0u, kb[0], kb[1]);
+        mma_bf16(s[nc], qa[2 * kp + 1][0], 0u, qa[2 * kp + 1][1], 0u, kb[2], kb[3]);
+      }
     }
-    __syncthreads();  // the stage is refilled two iterations later
+    // ---- online softmax on row g: this thread holds positions nc*8 + 2t, +1 ----
+    float sv[4];
+#pragma unroll
+    for (int nc = 0; nc < 2; ++nc) {
+      const int p0 = start + nc * 8 + 2 * t;
+      sv[nc * 2] = (p0 < t1) ? s[nc][0] : -INFINITY;
+      sv[nc * 2 + 1] = (p0 + 1 < t1) ? s[nc][1] : -INFINITY;
+    }
+    float tmax = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+    const float mnew = fmaxf(m, tmax);  // finite: every tile has at least one valid position
+    const float corr = exp2f(m - mnew);
+    float pv[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pv[i] = exp2f(sv[i] - mnew);
+    l = l * corr + (pv[0] + pv[1] + pv[2] + pv[3]);
+    m = mnew;
+    const uint32_t pa0 = pack2(pv[0], pv[1]);  // P[g][2t, 2t+1]
+    const uint32_t pa2 = pack2(pv[2], pv[3]);  // P[g][8 + 2t, +1]
+    // ---- O = O * corr + P V: 16 N-chunks of 8 dims ----
+#pragma unroll
+    for (int dp = 0; dp < 8; ++dp) {  // pairs of dim chunks
+      const int lj = lane >> 3;
+      const int row = (lj & 1) * 8 + (lane & 7);
+      const int chunk = dp * 2 + (lj >> 1);
+      uint32_t vb[4];
+      ldmatrix_x4_trans(sb + kTile * 256 + row * 256 + ((chunk ^ (row & 7)) << 4), vb);
+      o[2 * dp][0] *= corr; o[2 * dp][1] *= corr;
+      o[2 * dp + 1][0] *= corr; o[2 * dp + 1][1] *= corr;
+      mma_bf16(o[2 * dp], pa0, 0u, pa2, 0u, vb[0], vb[1]);
+      mma_bf16(o[2 * dp + 1], pa0, 0u, pa2, 0u, vb[2], vb[3]);
+    }
   }
-  const size_t slot = ((size_t)b * Hq + hq) * splits + sp;
-  float4* po = reinterpret_cast<float4*>(part_o + slot * kD + lane * 4);
-  *po = make_float4(acc[0], acc[1], acc[2], acc[3]);
-  if (lane == 0) {
-    part_ml[slot * 2] = m;
-    part_ml[slot * 2 + 1] = l;
+  cp_async_wait<0>();
+  // this thread's share of the row sum -> whole row
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
+
+  // ---- merge the four warps through shared memory (reusing the pipeline space) ----
+  __syncthreads();
+  float* sm_o = reinterpret_cast<float*>(smem_raw);                 // [warps][G][128]
+  float* sm_ml = sm_o + kAttnWarps * G * kD;                        // [warps][G][2]
+  if (g < G) {
+#pragma unroll
+    for (int dc = 0; dc < 16; ++dc) {
+      float2 v2 = make_float2(o[dc][0], o[dc][1]);
+      *reinterpret_cast<float2*>(&sm_o[((size_t)warp * G + g) * kD + dc * 8 + 2 * t]) = v2;
+    }
+    if (t == 0) {
+      sm_ml[(warp * G + g) * 2] = m;
+      sm_ml[(warp * G + g) * 2 + 1] = l;
+    }
+  }
+  __syncthreads();
+  // thread -> (head hh, 4 dims): G * 32 work items over 128 threads
+  for (int item = threadIdx.x; item < G * 32; item += kAttnWarps * 32) {
+    const int hh = item >> 5, d4 = (item & 31) * 4;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, sm_ml[(w * G + hh) * 2]);
+    float L = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float mw = sm_ml[(w * G + hh) * 2];
+      const float wgt = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+      L += wgt * sm_ml[(w * G + hh) * 2 + 1];
+      const float4 ov = *reinterpret_cast<const float4*>(&sm_o[((size_t)w * G + hh) * kD + d4]);
+      acc[0] += wgt * ov.x; acc[1] += wgt * ov.y; acc[2] += wgt * ov.z; acc[3] += wgt * ov.w;
+    }
+    const int hq = kh * G + hh;
+    if (splits == 1) {
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      uint2 raw;
+      raw.x = pack2(acc[0] * inv, acc[1] * inv);
+      raw.y = pack2(acc[2] * inv, acc[3] * inv);
+      *reinterpret_cast<uint2*>(out + ((size_t)b * Hq + hq) * kD + d4) = raw;
+    } else {
+      const size_t slot = ((size_t)b * Hq + hq) * splits + sp;
+      *reinterpret_cast<float4*>(part_o + slot * kD + d4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      if (d4 == 0) {
+        part_ml[slot * 2] = M;
+        part_ml[slot * 2 + 1] = L;
+      }
+    }
   }
 }
 
-// out[b, hq, :] = sum_s exp(m_s - M) * o_s / sum_s exp(m_s - M) * l_s
+// out[b, hq, :] = sum_s 2^(m_s - M) * o_s / sum_s 2^(m_s - M) * l_s  (log2 domain)
 // grid = (B, Hq), block = 32 (4 dims per lane)
 __global__ void k_attn_merge(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                              __nv_bfloat16* __restrict__ out, int Hq, int splits) {
@@ -201,17 +296,15 @@ __global__ void k_attn_merge(const float* __restrict__ part_o, const float* __re
   float L = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
   for (int s = 0; s < splits; ++s) {
     const float ms = part_ml[(base + s) * 2];
-    const float w = (ms == -INFINITY) ? 0.f : __expf(ms - M);
+    const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
     L += w * part_ml[(base + s) * 2 + 1];
     const float4 o = *reinterpret_cast<const float4*>(part_o + (base + s) * kD + lane * 4);
     acc[0] += w * o.x; acc[1] += w * o.y; acc[2] += w * o.z; acc[3] += w * o.w;
   }
   const float inv = L > 0.f ? 1.f / L : 0.f;
-  __nv_bfloat162 r0 = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv);
-  __nv_bfloat162 r1 = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
   uint2 raw;
-  raw.x = *reinterpret_cast<uint32_t*>(&r0);
-  raw.y = *reinterpret_cast<uint32_t*>(&r1);
+  raw.x = pack2(acc[0] * inv, acc[1] * inv);
+  raw.y = pack2(acc[2] * inv, acc[3] * inv);
   *reinterpret_cast<uint2*>(out + ((size_t)b * Hq + hq) * kD + lane * 4) = raw;
 }
 
@@ -317,10 +410,20 @@ cudaError_t launch_decode_attention(const void* qkv, const void* kcache, const v
   float* part_o = reinterpret_cast<float*>(workspace);
   float* part_ml = part_o + (size_t)B * Hq * splits * kD;
   dim3 grid(B, Hkv, splits);
-#define PENNY_ATTN(GG)                                                                          \
-  k_decode_attn<GG><<<grid, GG * 32, 0, stream>>>(                                              \
-      (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache,    \
-      positions, part_o, part_ml, Hq, Hkv, max_len, splits, scale)
+  cudaError_t rc = cudaSuccess;
+#define PENNY_ATTN(GG)                                                                            \
+  do {                                                                                            \
+    static bool attr_set = false;                                                                 \
+    if (!attr_set) {                                                                              \
+      rc = cudaFuncSetAttribute(k_decode_attn<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                kAttnSmem);                                                       \
+      if (rc != cudaSuccess) return rc;                                                           \
+      attr_set = true;                                                                            \
+    }                                                                                             \
+    k_decode_attn<GG><<<grid, kAttnWarps * 32, kAttnSmem, stream>>>(                              \
+        (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache,    \
+        positions, (__nv_bfloat16*)out, part_o, part_ml, Hq, Hkv, max_len, splits, scale);        \
+  } while (0)
   switch (G) {
     case 1: PENNY_ATTN(1); break;
     case 2: PENNY_ATTN(2); break;
@@ -329,8 +432,8 @@ cudaError_t launch_decode_attention(const void* qkv, const void* kcache, const v
     default: return cudaErrorInvalidValue;
   }
 #undef PENNY_ATTN
-  cudaError_t rc = cudaGetLastError();
-  if (rc != cudaSuccess) return rc;
+  rc = cudaGetLastError();
+  if (rc != cudaSuccess || splits == 1) return rc;
   k_attn_merge<<<dim3(B, Hq), 32, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, Hq, splits);
   return cudaGetLastError();
 }

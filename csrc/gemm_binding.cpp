@@ -1,8 +1,51 @@
-// Torch-facing functions of the tcgen05 GEMM family (standalone GEMM,
-// GEMM -> reduce-scatter, all-gather -> GEMM).
+// Torch-facing functions of the tcgen05 GEMM family (standalone GEMM here; the
+// fused GEMM -> reduce-scatter and all-gather -> GEMM are bound next to the
+// communicator because they need its heap).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
 #include <pybind11/pybind11.h>
 #include <torch/extension.h>
 
+#include "gemm_sm100.h"
+
 namespace py = pybind11;
 
-void bind_gemm(py::module_& m) { (void)m; }
+namespace {
+// One error word per device, zeroed at creation; a non-zero value means a
+// pipeline wait ran out inside a GEMM kernel.
+at::Tensor& error_word() {
+  static std::vector<at::Tensor> words(64);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!words[dev].defined())
+    words[dev] = torch::zeros({4}, torch::TensorOptions().dtype(torch::kInt32).device(torch::kCUDA, dev));
+  return words[dev];
+}
+}  // namespace
+
+uint32_t* penny_gemm_error_word() { return reinterpret_cast<uint32_t*>(error_word().data_ptr<int>()); }
+
+void bind_gemm(py::module_& m) {
+  // out[M, N] = a[M, K] @ b[N, K]^T (the nn.Linear convention: b is the weight)
+  m.def("gemm_bf16", [](at::Tensor a, at::Tensor b, at::Tensor out, int64_t block_n) {
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda(), "gemm_bf16: CUDA tensors");
+    TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 &&
+                    out.scalar_type() == at::kBFloat16, "gemm_bf16: bf16 only");
+    TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2, "gemm_bf16: 2-D tensors");
+    TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && out.stride(1) == 1, "gemm_bf16: rows must be contiguous");
+    const int64_t M = a.size(0), K = a.size(1), N = b.size(0);
+    TORCH_CHECK(b.size(1) == K && out.size(0) == M && out.size(1) == N, "gemm_bf16: shape mismatch");
+    const at::cuda::OptionalCUDAGuard guard(a.device());
+    cudaError_t rc = penny::sm100::launch_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, (int)a.stride(0), (int)b.stride(0),
+        (int)out.stride(0), (int)block_n, penny_gemm_error_word(), at::cuda::getCurrentCUDAStream().stream());
+    TORCH_CHECK(rc == cudaSuccess, "gemm_bf16: ", cudaGetErrorString(rc));
+  }, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("block_n") = 0);
+  // Synchronises; returns and clears the error code of the GEMM kernels (0 = fine).
+  m.def("gemm_error", []() {
+    at::Tensor& w = error_word();
+    int v = w[0].item<int>();
+    if (v != 0) w.zero_();
+    return v;
+  });
+}

@@ -1,0 +1,224 @@
+// The persistent tcgen05 GEMM kernel, parameterised by
+//   Ep    where finished rows go (local C, a peer's heap slot, ...) and what
+//         happens when a tile is complete (e.g. raise a cross-GPU flag),
+//   Gate  what the TMA producer must wait for before it may read the A rows of
+//         a tile (nothing, or a "rows have arrived from their owner" flag).
+// See gemm_sm100.cu for the role layout.
+#pragma once
+#include "gemm_sm100.cuh"
+
+namespace penny {
+namespace sm100 {
+
+constexpr int kBlockM = 128;
+constexpr int kGemmThreads = 192;  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+
+enum GemmError : uint32_t {
+  GEMM_OK = 0,
+  GEMM_ERR_PRODUCER_WAIT = 101,
+  GEMM_ERR_MMA_WAIT = 102,
+  GEMM_ERR_EPILOGUE_WAIT = 103,
+  GEMM_ERR_GATE_WAIT = 104,
+};
+
+struct GemmShape {
+  int M, N, K;
+  int tiles_m, tiles_n;
+  int m_rot;      // row-block rotation: tile row r works on block (r + m_rot) % tiles_m
+  int num_tiles;
+  int m_fastest;  // 1: consecutive tiles walk down M (share a B tile); 0: walk along N
+};
+
+template <int BN, class Ep, class Gate>
+struct GemmKernel {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = kBlockM * kBlockK * 2;
+  static constexpr int kBBytes = BN * kBlockK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = 2 * BN;  // two accumulators
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t parity,
+                                                    volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = gtime_ns();
+  for (uint32_t i = 1;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 0u) {
+      if (*abort_flag) return false;
+      if (gtime_ns() - t0 > kWaitNs) return false;
+    }
+  }
+}
+
+template <int BN, class Ep, class Gate>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const GemmShape s, const Ep ep, const Gate gate, uint32_t* error_word) {
+  using Cfg = GemmKernel<BN, Ep, Gate>;
+  constexpr int kStages = Cfg::kStages;
+  extern __shared__ unsigned char smem_raw[];
+  // tiles need 1024-byte alignment for the 128-byte swizzle
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + kStages * Cfg::kStageBytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + kStages;
+  uint64_t* tmem_full = bars + 2 * kStages;
+  uint64_t* tmem_empty = bars + 2 * kStages + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 4);  // one arrival per epilogue warp
+    }
+    *s_abort = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) tmem_alloc(tmem_holder, Cfg::kTmemCols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+  const int num_kb = (s.K + kBlockK - 1) / kBlockK;
+
+  auto decode = [&](int tile, int& m_blk, int& n_blk) {
+    int m_raw;
+    if (s.m_fastest) {
+      m_raw = tile % s.tiles_m;
+      n_blk = tile / s.tiles_m;
+    } else {
+      m_raw = tile / s.tiles_n;
+      n_blk = tile % s.tiles_n;
+    }
+    m_blk = (m_raw + s.m_rot) % s.tiles_m;
+  };
+  auto fail = [&](uint32_t code) {
+    *s_abort = 1;
+    atomicCAS(error_word, 0u, code);
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------ TMA producer
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = blockIdx.x; tile < s.num_tiles && !*s_abort; tile += gridDim.x) {
+        int m_blk, n_blk;
+        decode(tile, m_blk, n_blk);
+        if (!gate.wait_rows(m_blk, n_blk)) {
+          fail(GEMM_ERR_GATE_WAIT);
+          break;
+        }
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_abortable(&empty[stage], phase ^ 1u, s_abort)) {
+            ok = false;
+            break;
+          }
+          unsigned char* sa = tiles + stage * Cfg::kStageBytes;
+          mbar_expect_tx(&full[stage], Cfg::kStageBytes);
+          tma_load_2d(sa, &map_a, &full[stage], kb * kBlockK, m_blk * kBlockM);
+          tma_load_2d(sa + Cfg::kABytes, &map_b, &full[stage], kb * kBlockK, n_blk * BN);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) {
+          fail(GEMM_ERR_PRODUCER_WAIT);
+          break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // -------------------------------------------------------------- MMA issuer
+      constexpr uint32_t idesc = make_idesc_bf16(kBlockM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < s.num_tiles && !*s_abort; tile += gridDim.x, ++it) {
+        const int ab = it & 1;
+        const uint32_t ab_phase = (uint32_t)(it >> 1) & 1u;
+        bool ok = mbar_wait_abortable(&tmem_empty[ab], ab_phase ^ 1u, s_abort);
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(ab * BN);
+        for (int kb = 0; ok && kb < num_kb; ++kb) {
+          if (!mbar_wait_abortable(&full[stage], phase, s_abort)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(tiles + stage * Cfg::kStageBytes);
+          const uint64_t da = make_smem_desc(sa);
+          const uint64_t db = make_smem_desc(sa + Cfg::kABytes);
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k)
+            umma_bf16(d_tmem, advance_desc_k(da, k), advance_desc_k(db, k), idesc, (kb | k) != 0);
+          umma_commit(&empty[stage]);  // the slot is free once these MMAs have read it
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) {
+          fail(GEMM_ERR_MMA_WAIT);
+          break;
+        }
+        umma_commit(&tmem_full[ab]);  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // the TMEM lane quarter this warp may read
+    int it = 0;
+    for (int tile = blockIdx.x; tile < s.num_tiles && !*s_abort; tile += gridDim.x, ++it) {
+      int m_blk, n_blk;
+      decode(tile, m_blk, n_blk);
+      const int ab = it & 1;
+      const uint32_t ab_phase = (uint32_t)(it >> 1) & 1u;
+      if (!mbar_wait_abortable(&tmem_full[ab], ab_phase, s_abort)) {
+        if (lane == 0) fail(GEMM_ERR_EPILOGUE_WAIT);
+        break;
+      }
+      tc_fence_after_sync();
+      ep.tile_begin(m_blk, n_blk, tile);
+      const int row = m_blk * kBlockM + q * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (uint32_t)(ab * BN + c * 32) + ((uint32_t)(q * 32) << 16), r);
+        tmem_ld_wait();
+        uint32_t v[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = pack_bf16x2(r[2 * i], r[2 * i + 1]);
+        ep.store_row(row, n_blk * BN + c * 32, v, 32, s.M, s.N);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[ab]);
+      ep.tile_end(m_blk, n_blk, tile);
+    }
+  }
+  // ------------------------------------------------------------------- teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+}  // namespace sm100
+}  // namespace penny

@@ -31,6 +31,7 @@ CUDA_SOURCES = [
     "csrc/custom_all_reduce.cu",
     "csrc/comm.cu",
     "csrc/decode_kernels.cu",
+    "csrc/gemm_sm100.cu",
 ]
 CPP_SOURCES = [
     "csrc/torch_interface.cpp",

@@ -1,0 +1,40 @@
+"""The hand-written tcgen05 / TMEM / TMA GEMM against a PyTorch fp32 matmul."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def ref(a, b):
+    return a.float() @ b.float().t()
+
+
+@pytest.mark.parametrize("block_n", [128, 256])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (300, 520, 264), (1, 4096, 4096),
+                                   (64, 1792, 4096), (4096, 768, 4096), (1000, 3584, 1024)])
+def test_gemm_matches_fp32(shape, block_n):
+    from penny_b200._ext import ops
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + N * 3 + K)
+    a = (torch.randn(M, K, device="cuda", generator=g) * 0.5).bfloat16()
+    b = (torch.randn(N, K, device="cuda", generator=g) * 0.5).bfloat16()
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.gemm_bf16(a, b, out, block_n)
+    assert ops.gemm_error() == 0
+    want = ref(a, b)
+    # bf16 output rounding: relative 2^-8 of the value, plus accumulation-order noise
+    torch.testing.assert_close(out.float(), want, atol=2e-2 * (K ** 0.5) * 0.25 + 1e-2, rtol=1.6e-2)
+
+
+def test_gemm_strided_operands_and_repeat():
+    from penny_b200._ext import ops
+    M, N, K = 512, 384, 320
+    big_a = torch.randn(M, K + 64, device="cuda").bfloat16()
+    big_b = torch.randn(N, K + 128, device="cuda").bfloat16()
+    big_c = torch.zeros(M, N + 32, device="cuda", dtype=torch.bfloat16)
+    a, b, c = big_a[:, :K], big_b[:, 64:64 + K], big_c[:, :N]
+    for _ in range(3):
+        ops.gemm_bf16(a, b, c, 0)
+    assert ops.gemm_error() == 0
+    torch.testing.assert_close(c.float(), ref(a, b), atol=0.2, rtol=1.6e-2)
+    assert torch.all(big_c[:, N:] == 0)
