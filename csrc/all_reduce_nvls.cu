@@ -68,11 +68,17 @@ struct NvlsTwoShot {
     const size_t stride = (size_t)b.nblocks * b.nthreads;
     PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 1), s_abort);
     if (s_abort) return;
-    for (size_t j = (size_t)b.bid * b.nthreads + threadIdx.x; j < mine.end - mine.begin;
-         j += stride) {
-      const size_t v = mine.begin + j;
-      const V16 r = multimem_ld_reduce<T>(c.mc + a.in_heap_off + v * 16);
-      multimem_st(c.mc + a.out_heap_off + v * 16, r);
+    const size_t len = mine.end - mine.begin;
+    for (size_t j0 = (size_t)b.bid * b.nthreads + threadIdx.x; j0 < len; j0 += kBatch * stride) {
+      V16 r[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u)
+        if (j0 + u * stride < len)
+          r[u] = multimem_ld_reduce<T>(c.mc + a.in_heap_off + (mine.begin + j0 + u * stride) * 16);
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u)
+        if (j0 + u * stride < len)
+          multimem_st(c.mc + a.out_heap_off + (mine.begin + j0 + u * stride) * 16, r[u]);
     }
     PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 2), s_abort);
   }

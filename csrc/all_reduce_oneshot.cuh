@@ -42,12 +42,18 @@ struct OneShotFlag {
     const size_t stride = (size_t)b.nblocks * b.nthreads;
 
     PK_FOR_THREADS(b, tid) {
-      for (size_t v = (size_t)b.bid * b.nthreads + tid; v < V; v += stride) {
-        V16 x = load_user_vec<T>(in, v, a.n);
+      for (size_t v0 = (size_t)b.bid * b.nthreads + tid; v0 < V; v0 += kBatch * stride) {
+        V16 x[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u)
+          if (v0 + u * stride < V) x[u] = load_user_vec<T>(in, v0 + u * stride, a.n);
 #pragma unroll
         for (int d = 1; d < NG; ++d) {
           const int p = (rank + d) % NG;
-          st16(c.heap[p] + base + ((size_t)rank * V + v) * 16, x);
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u)
+            if (v0 + u * stride < V)
+              st16(c.heap[p] + base + ((size_t)rank * V + v0 + u * stride) * 16, x[u]);
         }
       }
     }

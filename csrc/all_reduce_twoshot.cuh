@@ -53,9 +53,16 @@ struct TwoShot {
       for (int d = 1; d < NG; ++d) {
         const int dst = (rank + d) % NG;  // start with a different peer on every rank
         const Span sp = split_span(V, NG, dst);
-        for (size_t j = first + tid; j < sp.end - sp.begin; j += stride) {
-          V16 x = load_user_vec<T>(in, sp.begin + j, a.n);
-          st16(c.heap[dst] + rs_off + ((size_t)rank * CV + j) * 16, x);
+        const size_t len = sp.end - sp.begin;
+        for (size_t j0 = first + tid; j0 < len; j0 += kBatch * stride) {
+          V16 x[kBatch];
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u)
+            if (j0 + u * stride < len) x[u] = load_user_vec<T>(in, sp.begin + j0 + u * stride, a.n);
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u)
+            if (j0 + u * stride < len)
+              st16(c.heap[dst] + rs_off + ((size_t)rank * CV + j0 + u * stride) * 16, x[u]);
         }
       }
     }
@@ -96,9 +103,15 @@ struct TwoShot {
       for (int d = 1; d < NG; ++d) {
         const int src = (rank + d) % NG;
         const Span sp = split_span(V, NG, src);
-        for (size_t j = first + tid; j < sp.end - sp.begin; j += stride) {
-          const size_t v = sp.begin + j;
-          store_user_vec<T>(out, v, a.n, ld16(c.heap[rank] + ag_off + v * 16));
+        const size_t len = sp.end - sp.begin;
+        for (size_t j0 = first + tid; j0 < len; j0 += kBatch * stride) {
+          V16 x[kBatch];
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u)
+            if (j0 + u * stride < len) x[u] = ld16(c.heap[rank] + ag_off + (sp.begin + j0 + u * stride) * 16);
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u)
+            if (j0 + u * stride < len) store_user_vec<T>(out, sp.begin + j0 + u * stride, a.n, x[u]);
         }
       }
     }
@@ -128,8 +141,16 @@ struct ReduceScatterPush {
       for (int d = 1; d < NG; ++d) {
         const int dst = (rank + d) % NG;
         const T* src = in + (size_t)dst * shard;
-        for (size_t j = first + tid; j < SV; j += stride)
-          st16(c.heap[dst] + base + ((size_t)rank * SV + j) * 16, load_user_vec<T>(src, j, shard));
+        for (size_t j0 = first + tid; j0 < SV; j0 += kBatch * stride) {
+          V16 x[kBatch];
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u)
+            if (j0 + u * stride < SV) x[u] = load_user_vec<T>(src, j0 + u * stride, shard);
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u)
+            if (j0 + u * stride < SV)
+              st16(c.heap[dst] + base + ((size_t)rank * SV + j0 + u * stride) * 16, x[u]);
+        }
       }
     }
     PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 1), s_abort);
@@ -175,13 +196,18 @@ struct AllGatherPush {
       PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 1), s_abort);
       if (s_abort) return;
       PK_FOR_THREADS(b, tid) {
-        for (size_t j = first + tid; j < SV; j += stride) {
-          V16 x = load_user_vec<T>(in, j, a.n);
+        for (size_t j0 = first + tid; j0 < SV; j0 += kBatch * stride) {
+          V16 x[kBatch];
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u)
+            if (j0 + u * stride < SV) x[u] = load_user_vec<T>(in, j0 + u * stride, a.n);
 #pragma unroll
           for (int d = 0; d < NG; ++d) {
             const int p = (rank + d) % NG;
             T* dst = reinterpret_cast<T*>(c.heap[p] + a.out_heap_off) + (size_t)rank * a.n;
-            store_user_vec<T>(dst, j, a.n, x);
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u)
+              if (j0 + u * stride < SV) store_user_vec<T>(dst, j0 + u * stride, a.n, x[u]);
           }
         }
       }
@@ -190,13 +216,20 @@ struct AllGatherPush {
     }
     const size_t base = scratch_half(a.scratch_off, a.scratch_bytes, seq);
     PK_FOR_THREADS(b, tid) {
-      for (size_t j = first + tid; j < SV; j += stride) {
-        V16 x = load_user_vec<T>(in, j, a.n);
-        store_user_vec<T>(out + (size_t)rank * a.n, j, a.n, x);
+      for (size_t j0 = first + tid; j0 < SV; j0 += kBatch * stride) {
+        V16 x[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u)
+          if (j0 + u * stride < SV) x[u] = load_user_vec<T>(in, j0 + u * stride, a.n);
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u)
+          if (j0 + u * stride < SV) store_user_vec<T>(out + (size_t)rank * a.n, j0 + u * stride, a.n, x[u]);
 #pragma unroll
         for (int d = 1; d < NG; ++d) {
           const int p = (rank + d) % NG;
-          st16(c.heap[p] + base + ((size_t)rank * SV + j) * 16, x);
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u)
+            if (j0 + u * stride < SV) st16(c.heap[p] + base + ((size_t)rank * SV + j0 + u * stride) * 16, x[u]);
         }
       }
     }
@@ -205,9 +238,15 @@ struct AllGatherPush {
     PK_FOR_THREADS(b, tid) {
       for (int d = 1; d < NG; ++d) {
         const int s = (rank + d) % NG;
-        for (size_t j = first + tid; j < SV; j += stride)
-          store_user_vec<T>(out + (size_t)s * a.n, j, a.n,
-                            ld16(c.heap[rank] + base + ((size_t)s * SV + j) * 16));
+        for (size_t j0 = first + tid; j0 < SV; j0 += kBatch * stride) {
+          V16 x[kBatch];
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u)
+            if (j0 + u * stride < SV) x[u] = ld16(c.heap[rank] + base + ((size_t)s * SV + j0 + u * stride) * 16);
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u)
+            if (j0 + u * stride < SV) store_user_vec<T>(out + (size_t)s * a.n, j0 + u * stride, a.n, x[u]);
+        }
       }
     }
   }

@@ -103,12 +103,20 @@ struct AllToAll {
     PK_FOR_THREADS(b, tid) {
       for (int d = 0; d < NG; ++d) {
         const int p = (rank + d) % NG;
-        for (size_t j = first + tid; j < CV; j += stride) {
-          V16 x = load_user_vec<T>(in + (size_t)p * a.n, j, a.n);
-          if (p == rank)
-            store_user_vec<T>(out + (size_t)rank * a.n, j, a.n, x);
-          else
-            st16(c.heap[p] + base + ((size_t)rank * CV + j) * 16, x);
+        for (size_t j0 = first + tid; j0 < CV; j0 += kBatch * stride) {
+          V16 x[kBatch];
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u)
+            if (j0 + u * stride < CV) x[u] = load_user_vec<T>(in + (size_t)p * a.n, j0 + u * stride, a.n);
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u) {
+            const size_t j = j0 + u * stride;
+            if (j >= CV) continue;
+            if (p == rank)
+              store_user_vec<T>(out + (size_t)rank * a.n, j, a.n, x[u]);
+            else
+              st16(c.heap[p] + base + ((size_t)rank * CV + j) * 16, x[u]);
+          }
         }
       }
     }

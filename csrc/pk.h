@@ -378,6 +378,10 @@ PK_DEV void store_user_vec(T* base, size_t v, size_t n, const V16& val) {
     if (v * E + i < n) base[v * E + i] = e[i];
 }
 
+// Vectors a thread keeps in flight per pass of a copy loop: the loads of a
+// batch are issued back to back before the first dependent store.
+constexpr int kBatch = 4;
+
 PK_HD size_t ceil_div(size_t a, size_t b) { return (a + b - 1) / b; }
 PK_HD size_t round_up(size_t a, size_t b) { return ceil_div(a, b) * b; }
 

@@ -24,7 +24,7 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from penny_b200.parallel.comm import ALGOS, ALGO_NAMES  # noqa: E402
-from penny_b200.utils import bench_device, bus_bandwidth_gbs, initialize_distributed, shutdown  # noqa: E402
+from penny_b200.utils import bench_device, bench_graph, bus_bandwidth_gbs, initialize_distributed, shutdown  # noqa: E402
 
 NVLINK_GBS = 900.0
 
@@ -46,6 +46,8 @@ def parse():
     p.add_argument("--bench-custom", action="store_true", help="also time penny.CustomAllreduce (<= 8 MiB)")
     p.add_argument("--profile-mode", default="none", choices=["none", "file"])
     p.add_argument("--heap-gib", type=float, default=6.0)
+    p.add_argument("--graph-inner", type=int, default=10,
+                   help="also time N back-to-back calls inside one CUDA graph (sizes <= 8 MiB); 0 = off")
     p.add_argument("--out", default="")
     return p.parse_args()
 
@@ -101,13 +103,19 @@ def main():
             x, y = src, torch.empty_like(src)
         ref = x.clone()
         dist.all_reduce(ref)
-        nccl_us = None
+        nccl_us, nccl_graph_us = None, None
         if not args.no_nccl:
             buf = x.clone()
             nccl_us = bench_device(lambda: dist.all_reduce(buf), args.warmup, args.num_tests)["median_us"]
             rec = {"op": "all_reduce", "impl": "nccl", "world": world, "dtype": args.dtype, "bytes": nbytes,
                    "t_us": round(nccl_us, 2),
                    "busbw_gbs": round(bus_bandwidth_gbs("all_reduce", nbytes, world, nccl_us), 2)}
+            if args.graph_inner > 0 and nbytes <= (8 << 20):
+                try:
+                    nccl_graph_us = bench_graph(lambda: dist.all_reduce(buf), args.graph_inner)["median_us"]
+                    rec["t_graph_us"] = round(nccl_graph_us, 2)
+                except RuntimeError:
+                    nccl_graph_us = None
             results.append(rec)
             if rank == 0:
                 print(json.dumps(rec), flush=True)
@@ -157,6 +165,14 @@ def main():
                 rec["blocks"], rec["threads"] = blocks, threads
             if nccl_us:
                 rec["vs_nccl"] = round(nccl_us / t, 3)
+            if args.graph_inner > 0 and nbytes <= (8 << 20):
+                def gcall():
+                    comm.all_reduce(x, out=y, algo=name, nnodes=nnodes, blocks=blocks, threads=threads)
+                tg = bench_graph(gcall, args.graph_inner)["median_us"]
+                comm.check()
+                rec["t_graph_us"] = round(tg, 2)
+                if nccl_graph_us:
+                    rec["vs_nccl_graph"] = round(nccl_graph_us / tg, 3)
             results.append(rec)
             if rank == 0:
                 print(json.dumps(rec), flush=True)

@@ -116,6 +116,46 @@ def bench_device(fn: Callable[[], None], warmup: int = 20, iters: int = 100, flu
             "max_us": times.max().item(), "iters": iters}
 
 
+def bench_graph(fn: Callable[[], None], inner: int = 10, warmup: int = 5, iters: int = 30, group=None) -> dict:
+    """Device time per call (us) with the CPU out of the picture: `inner`
+    back-to-back calls are captured in one CUDA graph and the replay is timed
+    (max over ranks).  This is what a serving engine pays per call inside its
+    decode graph; `bench_device` measures an eager call including its launch."""
+    import torch.distributed as dist
+    multi = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        fn()
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(inner):
+            fn()
+    for _ in range(warmup):
+        g.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        flush_l2()
+        if multi:
+            torch.cuda.synchronize()
+            dist.barrier(group=group)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3 / inner)
+    t = torch.tensor(times, dtype=torch.float64)
+    if multi:
+        tc = t.cuda()
+        dist.all_reduce(tc, op=dist.ReduceOp.MAX, group=group)
+        t = tc.cpu()
+    return {"mean_us": t.mean().item(), "median_us": t.median().item(), "min_us": t.min().item(), "inner": inner}
+
+
 def bench_kineto(fn, kernel_name: str, num_tests: int = 30, suppress_kineto_output: bool = False,
                  barrier_comm_profiling: bool = True):
     """Mean device time (us) of the kernels whose name contains `kernel_name`, taken
