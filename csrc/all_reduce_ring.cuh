@@ -284,7 +284,9 @@ struct DoubleRing {
     const int gpn = N / nnodes;
     const size_t V = ceil_div(a.n, E);
     const size_t half = scratch_half(a.scratch_off, a.scratch_bytes, seq);
-    const size_t slot_vecs = a.scratch_bytes / (4 * (size_t)b.nblocks * 16);
+    // sized from the call's shape, NOT from scratch_bytes: every call sharing a
+    // scratch region must cut it into the same two halves
+    const size_t slot_vecs = double_ring_slot_vecs(V, b.nblocks, N, nnodes);
     const Span seg = split_span(V, b.nblocks, b.bid);  // this block's contiguous piece
 
     RingPlan p;

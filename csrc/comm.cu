@@ -10,6 +10,7 @@
 #include "all_reduce_tree.cuh"
 #include "all_reduce_twoshot.cuh"
 #include "exchange.cuh"
+#include "gemm_fused_sm100.h"
 #include "launch.cuh"
 
 namespace penny {
@@ -259,9 +260,6 @@ void Communicator::run_all_reduce_once(int algo, int dtype, const void* const* i
       LaunchCfg cfg = cfg_for(V, t, stream, 64, 1);
       set_scratch(ensure(scratch_, double_ring_scratch_bytes(n, es, world_, nnodes, cfg.blocks),
                          "double ring"));
-      // the slot size is derived from scratch_bytes / blocks: lend exactly what this shape needs
-      for (int v = 0; v < nv; ++v)
-        a[v].scratch_bytes = double_ring_scratch_bytes(n, es, world_, nnodes, cfg.blocks);
       rc = launch_all_reduce_double_ring(dtype, ctx_, a, cfg);
       break;
     }
@@ -501,6 +499,49 @@ void Communicator::fused_ar_rmsnorm(int dtype, int proto, const void* const* in,
     cfg.blocks = t.blocks > 0 ? t.blocks : std::min(max_blocks, rows);
   }
   ckrt(launch_fused_ar_rmsnorm(dtype, proto, ctx_, a, cfg), "fused_ar_rmsnorm");
+}
+
+void Communicator::moe_dispatch(int dtype, const MoeArgs* args, const Tuning& t, cudaStream_t stream) {
+  LaunchCfg cfg;
+  cfg.threads = t.threads > 0 ? t.threads : 256;
+  cfg.stream = stream;
+  cfg.emu_world = emu_ ? world_ : 0;
+  const int cap = emu_ ? std::max(1, 128 / world_) : 64;  // every block polls blocks * world flags
+  cfg.blocks = std::min(cap, t.blocks > 0 ? t.blocks : cap);
+  ckrt(launch_moe_dispatch(dtype, ctx_, args, cfg), "moe_dispatch");
+}
+
+void Communicator::moe_combine(int dtype, const MoeArgs* args, const Tuning& t, cudaStream_t stream) {
+  LaunchCfg cfg;
+  cfg.threads = t.threads > 0 ? t.threads : 256;
+  cfg.stream = stream;
+  cfg.emu_world = emu_ ? world_ : 0;
+  const int cap = emu_ ? std::max(1, 128 / world_) : 64;
+  cfg.blocks = std::min(cap, t.blocks > 0 ? t.blocks : cap);
+  ckrt(launch_moe_combine(dtype, ctx_, args, cfg), "moe_combine");
+}
+
+void Communicator::gemm_reduce_scatter(const void* a, const void* b, void* out, int M, int N, int K,
+                                       int lda, int ldb, int ldo, uint32_t* error_word,
+                                       cudaStream_t stream) {
+  if (emu_ && world_ != 1) throw std::runtime_error("penny: fused GEMMs need one process per GPU");
+  Region& r = ensure(scratch_, sm100::gemm_rs_scratch_bytes(M, N, world_), "GEMM reduce-scatter");
+  ckrt(sm100::launch_gemm_rs(ctx_, r.off, r.bytes, a, b, out, M, N, K, lda, ldb, ldo, error_word, stream),
+       "gemm_reduce_scatter (M must be a multiple of 128 * world, N of 256, K and strides of 8)");
+}
+
+void Communicator::all_gather_gemm(const void* a_shard, const void* b, void* out, int M, int N, int K,
+                                   int lda, int ldb, int ldc, int side_ctas, uint32_t* error_word,
+                                   cudaStream_t stream) {
+  if (emu_ && world_ != 1) throw std::runtime_error("penny: fused GEMMs need one process per GPU");
+  const size_t need = sm100::ag_gemm_scratch_bytes(M, K);
+  if (ag_region_.bytes != need) {  // a new shape gets fresh memory: its halves must be exactly M x K
+    ag_region_.off = alloc(need);
+    ag_region_.bytes = need;
+  }
+  ckrt(sm100::launch_ag_gemm(ctx_, ag_region_.off, ag_region_.bytes, a_shard, b, out, M, N, K, lda, ldb,
+                             ldc, side_ctas, error_word, stream),
+       "all_gather_gemm (M must be a multiple of 128 * world, K and strides of 8)");
 }
 
 void Communicator::wait_selftest(cudaStream_t stream) {

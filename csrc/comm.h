@@ -89,6 +89,18 @@ class Communicator {
                         const void* weight, void* const* out, void* const* residual_out, int rows,
                         int hidden, float eps, const Tuning& t, cudaStream_t stream);
 
+  // MoE expert-parallel row exchange; args: views() entries (see MoeArgs).
+  void moe_dispatch(int dtype, const MoeArgs* args, const Tuning& t, cudaStream_t stream);
+  void moe_combine(int dtype, const MoeArgs* args, const Tuning& t, cudaStream_t stream);
+
+  // Fused tcgen05 GEMM + collective (bf16; real communicators, or an emulated
+  // world of 1).  out = this rank's [M / world, N] shard of sum_r A_r B_r^T.
+  void gemm_reduce_scatter(const void* a, const void* b, void* out, int M, int N, int K, int lda,
+                           int ldb, int ldo, uint32_t* error_word, cudaStream_t stream);
+  // out[M, N] = gather(a_shard)[M, K] * B[N, K]^T.
+  void all_gather_gemm(const void* a_shard, const void* b, void* out, int M, int N, int K, int lda,
+                       int ldb, int ldc, int side_ctas, uint32_t* error_word, cudaStream_t stream);
+
   // Largest n an all-reduce algorithm can take in one launch with the scratch
   // the heap can still provide (the host splits larger messages).
   int pick_algo(int dtype, size_t n) const;
@@ -121,6 +133,7 @@ class Communicator {
   Region scratch_ll_;    // halved, LL lines only
   Region scratch_pair_;  // exchange slot
   Region stage_in_, stage_out_;  // NVLS staging for tensors outside the heap
+  Region ag_region_;             // gathered A of all_gather_gemm, dedicated to one (M, K)
   bool destroyed_ = false;
 };
 

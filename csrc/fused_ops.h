@@ -32,6 +32,32 @@ inline size_t fused_norm_scratch_bytes(int proto, int rows, int hidden, int elem
   return (proto == FUSED_PROTO_LL ? 4 : 2) * (size_t)world * v * 16;
 }
 
+// MoE expert-parallel dispatch / combine (csrc/moe_dispatch_combine.cu).
+// Routing tables (device int32 arrays of this rank):
+//   order[i]            pair index (t * topk + k) of the i-th pair when sorted by expert
+//   expert_of_sorted[i] its expert
+//   send_off[e]         first sorted position of expert e (prefix sums, [experts + 1])
+//   dst_base[e]         row at expert e's owner where this rank's rows of e start
+//   dst_row_of_pair[p]  (written by dispatch) row of pair p at its expert's owner
+struct MoeArgs {
+  const void* x;         // dispatch: tokens [tokens, hidden]; combine: expert outputs [recv_rows, hidden]
+  void* out;             // combine: [tokens, hidden]
+  const int* order;
+  const int* expert_of_sorted;
+  const int* send_off;
+  const int* dst_base;
+  int* dst_row_of_pair;
+  const int* topk_ids;   // [tokens * topk]
+  const float* gates;    // [tokens * topk]
+  const int* meta;       // combine: this rank's copy of the return addresses [recv_rows]
+  size_t recv_off;       // heap offset of the symmetric receive rows [cap_rows, hidden]
+  size_t meta_off;       // heap offset of the symmetric return addresses [cap_rows] int32
+  size_t comb_off;       // heap offset of the symmetric combine slots [tokens * topk, hidden]
+  int tokens, topk, hidden, experts, cap_rows, recv_rows;
+};
+cudaError_t launch_moe_dispatch(int dtype, const CommCtx& c, const MoeArgs* a, const LaunchCfg& cfg);
+cudaError_t launch_moe_combine(int dtype, const CommCtx& c, const MoeArgs* a, const LaunchCfg& cfg);
+
 cudaError_t launch_add_rmsnorm(int dtype, const FusedNormArgs& a, int blocks, int threads,
                                cudaStream_t stream);
 cudaError_t launch_fused_ar_rmsnorm(int dtype, int proto, const CommCtx& c, const FusedNormArgs* a,

@@ -1,8 +1,12 @@
-// The persistent tcgen05 GEMM kernel, parameterised by
-//   Ep    where finished rows go (local C, a peer's heap slot, ...) and what
-//         happens when a tile is complete (e.g. raise a cross-GPU flag),
-//   Gate  what the TMA producer must wait for before it may read the A rows of
-//         a tile (nothing, or a "rows have arrived from their owner" flag).
+// The persistent tcgen05 GEMM kernel, parameterised by a Policy that says
+//   * which CTAs do side work instead of GEMM tiles (e.g. pushing A shards to
+//     the peers) and what that work is,
+//   * what the TMA producer must wait for before it may read the A rows of a
+//     tile (nothing, or a "rows have arrived from their owner" flag),
+//   * where finished rows go (local C, a peer's heap slot, ...) and what happens
+//     when a tile is complete (e.g. raise a cross-GPU flag),
+//   * what the epilogue warps do after their last tile (e.g. the reduction of a
+//     reduce-scatter) and how the call is closed.
 // See gemm_sm100.cu for the role layout.
 #pragma once
 #include "gemm_sm100.cuh"
@@ -29,7 +33,35 @@ struct GemmShape {
   int m_fastest;  // 1: consecutive tiles walk down M (share a B tile); 0: walk along N
 };
 
-template <int BN, class Ep, class Gate>
+// The policy of the plain GEMM; also documents the interface.  A policy may
+// replace State (what begin() returns and every hook receives) and any hook.
+struct PolicyBase {
+  struct State {};
+  int side_ctas = 0;
+  __device__ __forceinline__ State begin() const { return State{}; }
+  // all threads of a side CTA
+  template <class S>
+  __device__ __forceinline__ void side_work(const S&, int /*cta*/, int /*ncta*/, uint32_t*) const {}
+  // the producer thread, before the first A tile of a row block
+  template <class S>
+  __device__ __forceinline__ bool wait_rows(const S&, int /*m_blk*/, int /*n_blk*/) const { return true; }
+  // rows added to the A tile coordinate (A may live in one of two buffers)
+  template <class S>
+  __device__ __forceinline__ int a_row_offset(const S&) const { return 0; }
+  // the 128 epilogue threads
+  template <class S>
+  __device__ __forceinline__ void tile_begin(const S&, int, int) const {}
+  template <class S>
+  __device__ __forceinline__ void tile_end(const S&, int, int) const {}
+  template <class S>
+  __device__ __forceinline__ void after_tiles(const S&, int /*cta*/, int /*ncta*/, int /*tid*/,
+                                              uint32_t*) const {}
+  // every thread of every CTA, last thing in the kernel
+  template <class S>
+  __device__ __forceinline__ void finish(const S&) const {}
+};
+
+template <int BN>
 struct GemmKernel {
   static constexpr int kStages = (BN == 256) ? 4 : 6;
   static constexpr int kABytes = kBlockM * kBlockK * 2;
@@ -38,6 +70,21 @@ struct GemmKernel {
   static constexpr int kTmemCols = 2 * BN;  // two accumulators
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
 };
+
+// 32 bf16 (packed in 16 words) of one C row, bounds-checked.
+__device__ __forceinline__ void store_row_local(__nv_bfloat16* c, int ldc, int row, int col,
+                                                const uint32_t (&v)[16], int M, int N) {
+  if (row >= M) return;
+  __nv_bfloat16* dst = c + (size_t)row * ldc + col;
+  if (col + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      *reinterpret_cast<uint4*>(dst + i * 8) = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  } else {
+    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(v);
+    for (int i = 0; i < 32 && col + i < N; ++i) dst[i] = e[i];
+  }
+}
 
 __device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t parity,
                                                     volatile int* abort_flag) {
@@ -52,11 +99,19 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t pari
   }
 }
 
-template <int BN, class Ep, class Gate>
+template <int BN, class Policy>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                const GemmShape s, const Ep ep, const Gate gate, uint32_t* error_word) {
-  using Cfg = GemmKernel<BN, Ep, Gate>;
+                const GemmShape s, const Policy pol, uint32_t* error_word) {
+  using Cfg = GemmKernel<BN>;
+  const typename Policy::State st = pol.begin();
+  if ((int)blockIdx.x < pol.side_ctas) {
+    pol.side_work(st, blockIdx.x, pol.side_ctas, error_word);
+    pol.finish(st);
+    return;
+  }
+  const int cta = (int)blockIdx.x - pol.side_ctas;
+  const int ncta = (int)gridDim.x - pol.side_ctas;
   constexpr int kStages = Cfg::kStages;
   extern __shared__ unsigned char smem_raw[];
   // tiles need 1024-byte alignment for the 128-byte swizzle
@@ -113,10 +168,11 @@ gemm_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       // ------------------------------------------------------------ TMA producer
       int stage = 0;
       uint32_t phase = 0;
-      for (int tile = blockIdx.x; tile < s.num_tiles && !*s_abort; tile += gridDim.x) {
+      const int a_row0 = pol.a_row_offset(st);
+      for (int tile = cta; tile < s.num_tiles && !*s_abort; tile += ncta) {
         int m_blk, n_blk;
         decode(tile, m_blk, n_blk);
-        if (!gate.wait_rows(m_blk, n_blk)) {
+        if (!pol.wait_rows(st, m_blk, n_blk)) {
           fail(GEMM_ERR_GATE_WAIT);
           break;
         }
@@ -128,7 +184,7 @@ gemm_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           }
           unsigned char* sa = tiles + stage * Cfg::kStageBytes;
           mbar_expect_tx(&full[stage], Cfg::kStageBytes);
-          tma_load_2d(sa, &map_a, &full[stage], kb * kBlockK, m_blk * kBlockM);
+          tma_load_2d(sa, &map_a, &full[stage], kb * kBlockK, a_row0 + m_blk * kBlockM);
           tma_load_2d(sa + Cfg::kABytes, &map_b, &full[stage], kb * kBlockK, n_blk * BN);
           if (++stage == kStages) {
             stage = 0;
@@ -148,7 +204,7 @@ gemm_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
-      for (int tile = blockIdx.x; tile < s.num_tiles && !*s_abort; tile += gridDim.x, ++it) {
+      for (int tile = cta; tile < s.num_tiles && !*s_abort; tile += ncta, ++it) {
         const int ab = it & 1;
         const uint32_t ab_phase = (uint32_t)(it >> 1) & 1u;
         bool ok = mbar_wait_abortable(&tmem_empty[ab], ab_phase ^ 1u, s_abort);
@@ -183,7 +239,7 @@ gemm_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;  // the TMEM lane quarter this warp may read
     int it = 0;
-    for (int tile = blockIdx.x; tile < s.num_tiles && !*s_abort; tile += gridDim.x, ++it) {
+    for (int tile = cta; tile < s.num_tiles && !*s_abort; tile += ncta, ++it) {
       int m_blk, n_blk;
       decode(tile, m_blk, n_blk);
       const int ab = it & 1;
@@ -193,7 +249,7 @@ gemm_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         break;
       }
       tc_fence_after_sync();
-      ep.tile_begin(m_blk, n_blk, tile);
+      pol.tile_begin(st, m_blk, n_blk);
       const int row = m_blk * kBlockM + q * 32 + lane;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -203,13 +259,14 @@ gemm_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         uint32_t v[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] = pack_bf16x2(r[2 * i], r[2 * i + 1]);
-        ep.store_row(row, n_blk * BN + c * 32, v, 32, s.M, s.N);
+        pol.store_row(st, row, n_blk * BN + c * 32, v, s.M, s.N);
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[ab]);
-      ep.tile_end(m_blk, n_blk, tile);
+      pol.tile_end(st, m_blk, n_blk);
     }
+    pol.after_tiles(st, cta, ncta, (int)threadIdx.x - 64, error_word);
   }
   // ------------------------------------------------------------------- teardown
   tc_fence_before_sync();
@@ -218,6 +275,7 @@ gemm_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
+  pol.finish(st);
 }
 
 }  // namespace sm100

@@ -71,30 +71,14 @@ cudaError_t make_tile_map(CUtensorMap* map, const void* base, uint64_t rows, uin
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-// Plain epilogue: C row-major in this GPU's memory.
-struct StoreLocal {
+// Plain GEMM: C row-major in this GPU's memory, nothing to wait for.
+struct StoreLocal : PolicyBase {
   __nv_bfloat16* c;
   int ldc;
-  __device__ __forceinline__ void tile_begin(int, int, int) const {}
-  __device__ __forceinline__ void store_row(int row, int col, const uint32_t (&v)[16], int ncols,
+  __device__ __forceinline__ void store_row(const State&, int row, int col, const uint32_t (&v)[16],
                                             int M, int N) const {
-    if (row >= M) return;
-    __nv_bfloat16* dst = c + (size_t)row * ldc + col;
-    if (col + 32 <= N && ncols == 32 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        *reinterpret_cast<uint4*>(dst + i * 8) = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-    } else {
-      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(v);
-      for (int i = 0; i < 32 && col + i < N; ++i) dst[i] = e[i];
-    }
+    store_row_local(c, ldc, row, col, v, M, N);
   }
-  __device__ __forceinline__ void tile_end(int, int, int) const {}
-};
-
-// The producer of the plain GEMM never waits for anything but ring slots.
-struct NoGate {
-  __device__ __forceinline__ bool wait_rows(int, int) const { return true; }
 };
 
 template <int BN>
@@ -105,10 +89,10 @@ cudaError_t launch_gemm_bn(const void* a, const void* b, void* c, int M, int N, 
   if (rc != cudaSuccess) return rc;
   rc = make_tile_map(&mb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN);
   if (rc != cudaSuccess) return rc;
-  using Kernel = GemmKernel<BN, StoreLocal, NoGate>;
+  using Kernel = GemmKernel<BN>;
   static bool attr = false;
   if (!attr) {
-    rc = cudaFuncSetAttribute(gemm_persistent<BN, StoreLocal, NoGate>,
+    rc = cudaFuncSetAttribute(gemm_persistent<BN, StoreLocal>,
                               cudaFuncAttributeMaxDynamicSharedMemorySize, Kernel::kSmemBytes);
     if (rc != cudaSuccess) return rc;
     attr = true;
@@ -116,9 +100,11 @@ cudaError_t launch_gemm_bn(const void* a, const void* b, void* c, int M, int N, 
   const int tiles_m = (M + kBlockM - 1) / kBlockM, tiles_n = (N + BN - 1) / BN;
   const int grid = std::min(sms, tiles_m * tiles_n);
   GemmShape shape{M, N, K, tiles_m, tiles_n, 0, tiles_m * tiles_n, 1};
-  StoreLocal ep{reinterpret_cast<__nv_bfloat16*>(c), ldc};
-  gemm_persistent<BN, StoreLocal, NoGate><<<grid, kGemmThreads, Kernel::kSmemBytes, stream>>>(
-      ma, mb, shape, ep, NoGate{}, error_word);
+  StoreLocal ep;
+  ep.c = reinterpret_cast<__nv_bfloat16*>(c);
+  ep.ldc = ldc;
+  gemm_persistent<BN, StoreLocal><<<grid, kGemmThreads, Kernel::kSmemBytes, stream>>>(
+      ma, mb, shape, ep, error_word);
   return cudaGetLastError();
 }
 

@@ -31,6 +31,7 @@ using namespace penny;
 void bind_custom_all_reduce(py::module_& m);  // custom_all_reduce_binding.cpp
 void bind_gemm(py::module_& m);               // gemm_binding.cpp
 void bind_decode(py::module_& m);             // decode_binding.cpp
+uint32_t* penny_gemm_error_word();            // gemm_binding.cpp
 
 namespace {
 
@@ -376,6 +377,120 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     TORCH_CHECK(rc == cudaSuccess, "penny: add_rmsnorm: ", cudaGetErrorString(rc));
   }, py::arg("x"), py::arg("residual"), py::arg("weight"), py::arg("out"),
      py::arg("residual_out"), py::arg("eps") = 1e-5);
+
+  // MoE dispatch: x rows -> the owners of their experts.  Every list has one entry
+  // per view.  recv / meta are symmetric heap tensors ([cap_rows, hidden], [cap_rows] int32).
+  m.def("comm_moe_dispatch", [](int64_t h, std::vector<at::Tensor> x, std::vector<at::Tensor> order,
+                                std::vector<at::Tensor> expert_of_sorted, std::vector<at::Tensor> send_off,
+                                std::vector<at::Tensor> dst_base, std::vector<at::Tensor> dst_row_of_pair,
+                                std::vector<at::Tensor> recv, std::vector<at::Tensor> meta, int topk,
+                                int experts, int blocks) {
+    Communicator* c = as_comm(h);
+    const int nv = c->views();
+    TORCH_CHECK((int)x.size() == nv && (int)recv.size() == nv && (int)meta.size() == nv, "comm_moe_dispatch: views");
+    MoeArgs a[kMaxRanks];
+    memset(a, 0, sizeof(a));
+    for (int v = 0; v < nv; ++v) {
+      check_dense(x[v], "x");
+      TORCH_CHECK(x[v].dim() == 2 && recv[v].dim() == 2 && recv[v].size(1) == x[v].size(1), "comm_moe_dispatch: shapes");
+      for (const at::Tensor* t : {&order[v], &expert_of_sorted[v], &send_off[v], &dst_base[v], &dst_row_of_pair[v], &meta[v]})
+        TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->is_contiguous(), "comm_moe_dispatch: int32 CUDA tables");
+      a[v].x = x[v].data_ptr();
+      a[v].order = order[v].data_ptr<int>();
+      a[v].expert_of_sorted = expert_of_sorted[v].data_ptr<int>();
+      a[v].send_off = send_off[v].data_ptr<int>();
+      a[v].dst_base = dst_base[v].data_ptr<int>();
+      a[v].dst_row_of_pair = dst_row_of_pair[v].data_ptr<int>();
+      a[v].recv_off = c->heap_offset_of(recv[v].data_ptr(), v);
+      a[v].meta_off = c->heap_offset_of(meta[v].data_ptr(), v);
+      TORCH_CHECK(a[v].recv_off != kNotInHeap && a[v].meta_off != kNotInHeap,
+                  "comm_moe_dispatch: recv and meta must be symmetric heap tensors");
+      TORCH_CHECK(a[v].recv_off == a[0].recv_off && a[v].meta_off == a[0].meta_off, "comm_moe_dispatch: offsets differ");
+      a[v].tokens = (int)x[v].size(0);
+      a[v].topk = topk;
+      a[v].hidden = (int)x[v].size(1);
+      a[v].experts = experts;
+      a[v].cap_rows = (int)recv[v].size(0);
+    }
+    const at::cuda::OptionalCUDAGuard guard(x[0].device());
+    Tuning t;
+    t.blocks = blocks;
+    c->moe_dispatch(dtype_of(x[0]), a, t, current_stream());
+  }, py::arg("comm"), py::arg("x"), py::arg("order"), py::arg("expert_of_sorted"), py::arg("send_off"),
+     py::arg("dst_base"), py::arg("dst_row_of_pair"), py::arg("recv"), py::arg("meta"), py::arg("topk"),
+     py::arg("experts"), py::arg("blocks") = 0);
+
+  // MoE combine: expert outputs y (rows as received) -> out[t] = sum_k gates[t, k] * y[t, k].
+  m.def("comm_moe_combine", [](int64_t h, std::vector<at::Tensor> y, std::vector<at::Tensor> out,
+                               std::vector<at::Tensor> topk_ids, std::vector<at::Tensor> gates,
+                               std::vector<at::Tensor> meta, std::vector<at::Tensor> dst_row_of_pair,
+                               std::vector<at::Tensor> comb, std::vector<int> recv_rows, int experts,
+                               int blocks) {
+    Communicator* c = as_comm(h);
+    const int nv = c->views();
+    TORCH_CHECK((int)y.size() == nv && (int)out.size() == nv && (int)comb.size() == nv && (int)recv_rows.size() == nv,
+                "comm_moe_combine: views");
+    MoeArgs a[kMaxRanks];
+    memset(a, 0, sizeof(a));
+    for (int v = 0; v < nv; ++v) {
+      check_dense(y[v], "y");
+      check_dense(out[v], "out");
+      TORCH_CHECK(topk_ids[v].scalar_type() == at::kInt && gates[v].scalar_type() == at::kFloat &&
+                      meta[v].scalar_type() == at::kInt && dst_row_of_pair[v].scalar_type() == at::kInt,
+                  "comm_moe_combine: table dtypes (int32 ids/meta/rows, fp32 gates)");
+      TORCH_CHECK(topk_ids[v].is_contiguous() && gates[v].is_contiguous(), "comm_moe_combine: contiguous tables");
+      a[v].x = y[v].data_ptr();
+      a[v].out = out[v].data_ptr();
+      a[v].topk_ids = topk_ids[v].data_ptr<int>();
+      a[v].gates = gates[v].data_ptr<float>();
+      a[v].meta = meta[v].data_ptr<int>();
+      a[v].dst_row_of_pair = dst_row_of_pair[v].data_ptr<int>();
+      a[v].comb_off = c->heap_offset_of(comb[v].data_ptr(), v);
+      TORCH_CHECK(a[v].comb_off != kNotInHeap && a[v].comb_off == c->heap_offset_of(comb[0].data_ptr(), 0),
+                  "comm_moe_combine: comb must be a symmetric heap tensor");
+      a[v].tokens = (int)out[v].size(0);
+      a[v].topk = (int)(topk_ids[v].numel() / out[v].size(0));
+      a[v].hidden = (int)out[v].size(1);
+      a[v].experts = experts;
+      a[v].recv_rows = recv_rows[v];
+      TORCH_CHECK(y[v].size(0) >= recv_rows[v] && comb[v].size(0) >= (int64_t)a[v].tokens * a[v].topk,
+                  "comm_moe_combine: buffer sizes");
+    }
+    const at::cuda::OptionalCUDAGuard guard(y[0].device());
+    Tuning t;
+    t.blocks = blocks;
+    c->moe_combine(dtype_of(out[0]), a, t, current_stream());
+  }, py::arg("comm"), py::arg("y"), py::arg("out"), py::arg("topk_ids"), py::arg("gates"), py::arg("meta"),
+     py::arg("dst_row_of_pair"), py::arg("comb"), py::arg("recv_rows"), py::arg("experts"), py::arg("blocks") = 0);
+
+  // out[M / world, N] = this rank's row shard of sum_r a_r[M, K_r] @ b_r[N, K_r]^T
+  m.def("comm_gemm_rs", [](int64_t h, at::Tensor a, at::Tensor b, at::Tensor out) {
+    Communicator* c = as_comm(h);
+    TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 &&
+                    out.scalar_type() == at::kBFloat16, "comm_gemm_rs: bf16 CUDA tensors");
+    TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 &&
+                    out.stride(1) == 1, "comm_gemm_rs: 2-D tensors with contiguous rows");
+    const int64_t M = a.size(0), K = a.size(1), N = b.size(0);
+    TORCH_CHECK(b.size(1) == K && out.size(0) * c->world() == M && out.size(1) == N, "comm_gemm_rs: shapes");
+    const at::cuda::OptionalCUDAGuard guard(a.device());
+    c->gemm_reduce_scatter(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K,
+                           (int)a.stride(0), (int)b.stride(0), (int)out.stride(0), penny_gemm_error_word(),
+                           current_stream());
+  });
+  // out[M, N] = all_gather(a_shard)[M, K] @ b[N, K]^T
+  m.def("comm_ag_gemm", [](int64_t h, at::Tensor a_shard, at::Tensor b, at::Tensor out, int side_ctas) {
+    Communicator* c = as_comm(h);
+    TORCH_CHECK(a_shard.is_cuda() && a_shard.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 &&
+                    out.scalar_type() == at::kBFloat16, "comm_ag_gemm: bf16 CUDA tensors");
+    TORCH_CHECK(a_shard.dim() == 2 && b.dim() == 2 && out.dim() == 2 && a_shard.stride(1) == 1 &&
+                    b.stride(1) == 1 && out.stride(1) == 1, "comm_ag_gemm: 2-D tensors with contiguous rows");
+    const int64_t M = a_shard.size(0) * c->world(), K = a_shard.size(1), N = b.size(0);
+    TORCH_CHECK(b.size(1) == K && out.size(0) == M && out.size(1) == N, "comm_ag_gemm: shapes");
+    const at::cuda::OptionalCUDAGuard guard(a_shard.device());
+    c->all_gather_gemm(a_shard.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K,
+                       (int)a_shard.stride(0), (int)b.stride(0), (int)out.stride(0), side_ctas,
+                       penny_gemm_error_word(), current_stream());
+  }, py::arg("comm"), py::arg("a_shard"), py::arg("b"), py::arg("out"), py::arg("side_ctas") = 0);
 
   m.def("comm_wait_selftest", [](int64_t h) { as_comm(h)->wait_selftest(current_stream()); });
   m.def("comm_status", [](int64_t h, int view, bool clear) {

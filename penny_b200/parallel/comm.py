@@ -221,6 +221,47 @@ class Communicator:
                                   blocks, threads, sym)
         return self._ret(outs), (self._ret(rout) if rout else None)
 
+    # ---------------------------------------------------------------------- MoE
+    def moe_dispatch(self, x, order, expert_of_sorted, send_off, dst_base, dst_row_of_pair, recv, meta,
+                     topk: int, experts: int, blocks: int = 0):
+        """Pushes every (token, k) row of `x` to the rank that owns its expert, into
+        the symmetric tensors `recv` (rows) and `meta` (return addresses).  The
+        routing tables come from penny_b200.models.moe_ep.build_routing."""
+        L = self._as_list
+        ops.comm_moe_dispatch(self._h, L(x), L(order), L(expert_of_sorted), L(send_off), L(dst_base),
+                              L(dst_row_of_pair), L(recv), L(meta), int(topk), int(experts), blocks)
+
+    def moe_combine(self, y, out, topk_ids, gates, meta, dst_row_of_pair, comb, recv_rows, experts: int,
+                    blocks: int = 0):
+        """Returns the expert outputs `y` to their sources and forms
+        out[t] = sum_k gates[t, k] * y[t, k] in the same kernel."""
+        L = self._as_list
+        rr = [int(recv_rows)] if isinstance(recv_rows, int) else [int(r) for r in recv_rows]
+        ops.comm_moe_combine(self._h, L(y), L(out), L(topk_ids), L(gates), L(meta), L(dst_row_of_pair),
+                             L(comb), rr, int(experts), blocks)
+
+    def gemm_reduce_scatter(self, a: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None):
+        """Row-parallel linear fused with its reduce-scatter (one tcgen05 kernel):
+        out[M / world, N] = this rank's row shard of sum_r a_r[M, K_r] @ weight_r[N, K_r]^T."""
+        if out is None:
+            out = torch.empty(a.shape[0] // self.world_size, weight.shape[0], dtype=a.dtype, device=a.device)
+        ops.comm_gemm_rs(self._h, a, weight, out)
+        return out
+
+    def all_gather_gemm(self, a_shard: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
+                        side_ctas: int = 0):
+        """Column-parallel linear fused with the all-gather of its input (one
+        tcgen05 kernel): out[M, N] = all_gather(a_shard)[M, K] @ weight[N, K]^T."""
+        if out is None:
+            out = torch.empty(a_shard.shape[0] * self.world_size, weight.shape[0], dtype=a_shard.dtype,
+                              device=a_shard.device)
+        ops.comm_ag_gemm(self._h, a_shard, weight, out, side_ctas)
+        return out
+
+    def gemm_error(self) -> int:
+        """Synchronises; non-zero if a pipeline wait inside a GEMM kernel ran out."""
+        return ops.gemm_error()
+
     # ------------------------------------------------------------------- status
     def status(self, view: int = 0, clear: bool = True) -> dict:
         return dict(ops.comm_status(self._h, view, clear))

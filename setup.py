@@ -32,6 +32,8 @@ CUDA_SOURCES = [
     "csrc/comm.cu",
     "csrc/decode_kernels.cu",
     "csrc/gemm_sm100.cu",
+    "csrc/gemm_fused_sm100.cu",
+    "csrc/moe_dispatch_combine.cu",
 ]
 CPP_SOURCES = [
     "csrc/torch_interface.cpp",

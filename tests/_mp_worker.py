@@ -166,6 +166,34 @@ def main():
         assert torch.allclose(y.float(), torch.full_like(y, s * world).float()), y[:4]
     check("cuda_graph_replay", run_graph)
 
+    # ---- fused tcgen05 GEMM + collective ----
+    def run_fused_gemm():
+        import penny_cpp
+        M, N, Kfull = 128 * world * 2, 512, 256 * world
+        g = torch.Generator(device="cuda").manual_seed(4242)
+        a_full = (torch.randn(M, Kfull, device="cuda", generator=g) * 0.5).bfloat16()   # same on all ranks
+        w_full = (torch.randn(N, Kfull, device="cuda", generator=g) * 0.5).bfloat16()
+        ks = Kfull // world
+        a_r, w_r = a_full[:, rank * ks:(rank + 1) * ks].contiguous(), w_full[:, rank * ks:(rank + 1) * ks].contiguous()
+        want = a_full.float() @ w_full.float().t()
+        rows = M // world
+        for _ in range(3):
+            out = comm.gemm_reduce_scatter(a_r, w_r)
+            assert penny_cpp.gemm_error() == 0
+            comm.check()
+            torch.testing.assert_close(out.float(), want[rank * rows:(rank + 1) * rows], atol=0.3, rtol=2e-2)
+        # all-gather -> GEMM: rows sharded, weight column shard
+        nl = N // world if (N // world) % 8 == 0 else N
+        w_col = w_full[rank * nl:(rank + 1) * nl] if nl != N else w_full
+        a_shard = a_full[rank * rows:(rank + 1) * rows].contiguous()
+        for _ in range(3):
+            out = comm.all_gather_gemm(a_shard, w_col.contiguous())
+            assert penny_cpp.gemm_error() == 0
+            comm.check()
+            ref_rows = want[:, rank * nl:(rank + 1) * nl] if nl != N else want
+            torch.testing.assert_close(out.float(), ref_rows, atol=0.3, rtol=2e-2)
+    check("fused_gemm", run_fused_gemm)
+
     # ---- tensor-parallel decoder vs the same model on one GPU ----
     def run_tp_decode():
         from penny_b200.models.llama_tp import LlamaConfig, LlamaTPDecoder

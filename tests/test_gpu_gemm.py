@@ -38,3 +38,32 @@ def test_gemm_strided_operands_and_repeat():
     assert ops.gemm_error() == 0
     torch.testing.assert_close(c.float(), ref(a, b), atol=0.2, rtol=1.6e-2)
     assert torch.all(big_c[:, N:] == 0)
+
+
+def test_fused_gemm_kernels_single_rank():
+    """GEMM -> reduce-scatter and all-gather -> GEMM with a world of one: the heap
+    slots, per-tile flags, the TMA loads from the gathered buffer and the call
+    counter all run; only the NVLink hop is missing."""
+    from penny_b200._ext import ops
+    from penny_b200.parallel.comm import Communicator
+    comm = Communicator.emulated(1, heap_bytes=256 << 20, timeout_ms=2000)
+    try:
+        for it in range(3):  # both scratch halves
+            M, N, K = 512, 768, 320
+            a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+            w = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+            out = comm.gemm_reduce_scatter(a, w)
+            assert ops.gemm_error() == 0
+            comm.check()
+            torch.testing.assert_close(out.float(), ref(a, w), atol=0.15, rtol=1.6e-2)
+            out2 = comm.all_gather_gemm(a, w)
+            assert ops.gemm_error() == 0
+            comm.check()
+            torch.testing.assert_close(out2.float(), ref(a, w), atol=0.15, rtol=1.6e-2)
+            N2 = 200  # narrow, ragged N for the gathered variant
+            w2 = (torch.randn(N2, K, device="cuda") * 0.5).bfloat16()
+            out3 = comm.all_gather_gemm(a, w2, side_ctas=3)
+            assert ops.gemm_error() == 0
+            torch.testing.assert_close(out3.float(), ref(a, w2), atol=0.15, rtol=1.6e-2)
+    finally:
+        comm.close()
