@@ -106,7 +106,7 @@ def run_penny(args):
     import torch.distributed as dist
     sys.path.insert(0, ROOT)
     from penny_b200.models.llama_tp import LlamaConfig, LlamaTPDecoder
-    from penny_b200.utils import initialize_distributed, shutdown
+    from penny_b200.utils import initialize_distributed
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
@@ -187,8 +187,7 @@ def run_penny(args):
                     "h2d_bytes_per_step": args.batch * 8, "d2h_bytes_per_step": args.batch * 8},
             "gpu_launches": model.kernels_per_step * args.steps,
         }), flush=True)
-    if world > 1:
-        shutdown()
+    _leave(comm, world)
 
 
 def run_reference(args):
@@ -200,6 +199,7 @@ def run_reference(args):
     sys.path = [ref_dir] + [p for p in sys.path if os.path.abspath(p or ".") != ROOT]
     os.environ.setdefault("NNODES", "1")
     os.environ.setdefault("NVSHMEM_REMOTE_TRANSPORT", "none")
+    os.environ.setdefault("NVSHMEM_DISABLE_NVLS", "1")  # no multicast binding to tear down at exit
     import math
     import torch
     import torch.distributed as dist
@@ -381,13 +381,30 @@ def run_reference(args):
                     "d2h_bytes_per_step": B * 8},
             "gpu_launches": 0,
         }), flush=True)
+    _leave(None, world)
+
+
+def _leave(comm, world):
+    """Ends the process without the collective tear-downs of torch.distributed /
+    NVSHMEM, which were seen to block for minutes after CUDA graphs containing
+    their kernels (the numbers are already printed).  The native communicator IS
+    closed first: its heap must be unbound from the NVLS multicast object on every
+    rank before any rank's process goes away."""
+    import torch
+    torch.cuda.synchronize()
+    if comm is not None:
+        comm.barrier()
+        comm.close()
+    sys.stdout.flush()
+    sys.stderr.flush()
     if world > 1:
+        import torch.distributed as dist
         try:
-            car.close()
+            dist.barrier()  # everyone has finished its GPU work
+            torch.cuda.synchronize()
         except Exception:  # noqa: BLE001
             pass
-        dist.barrier()
-        dist.destroy_process_group()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -140,9 +140,13 @@ int Communicator::pick_algo(int dtype, size_t n) const {
   if (world_ < 2) return ALGO_ONESHOT;
   const bool even = (world_ == 2 || world_ == 4 || world_ == 6 || world_ == 8);
   if (!even) return ALGO_RING_STANDARD;
+  // Measured on 8 x B200 (device time per call inside a CUDA graph): the
+  // flag-in-data protocol wins up to 32 KiB (9-11 us), the switch reduction from
+  // there on (17 us at 256 KiB, 826 GB/s bus bandwidth at 1 GiB); without a
+  // multicast mapping the pushes take over (one-shot to 256 KiB, then two-shot).
   if (bytes <= (size_t)32 << 10) return ALGO_ONESHOT_LL;
-  if (bytes <= (size_t)256 << 10) return ALGO_ONESHOT;
   if (has_multicast()) return ALGO_NVLS;
+  if (bytes <= (size_t)256 << 10) return ALGO_ONESHOT;
   return ALGO_TWOSHOT;
 }
 

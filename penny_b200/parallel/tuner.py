@@ -24,8 +24,8 @@ DEFAULT_CACHE = os.path.join(os.path.expanduser("~"), ".cache", "penny_b200", "t
 # Symmetric (heap) tensors may use "nvls" without staging; others fall back to "twoshot".
 BUILTIN: Dict[str, List[Tuple[Optional[int], str]]] = {
     "2": [(64 << 10, "oneshot_ll"), (2 << 20, "oneshot"), (None, "twoshot")],
-    "4": [(32 << 10, "oneshot_ll"), (512 << 10, "oneshot"), (None, "nvls")],
-    "8": [(32 << 10, "oneshot_ll"), (256 << 10, "oneshot"), (None, "nvls")],
+    "4": [(32 << 10, "oneshot_ll"), (None, "nvls")],
+    "8": [(32 << 10, "oneshot_ll"), (None, "nvls")],
 }
 
 
@@ -91,5 +91,5 @@ class Tuner:
         bounds = [b if b is not None else float("inf") for b, _ in rows]
         algo = rows[min(bisect_left(bounds, nbytes), len(rows) - 1)][1]
         if algo.startswith("nvls") and not has_multicast:
-            algo = "twoshot" if algo == "nvls" else "oneshot"
+            algo = "oneshot" if nbytes <= (256 << 10) else "twoshot"
         return algo
