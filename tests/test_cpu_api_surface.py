@@ -1,0 +1,64 @@
+"""The Python-visible surface a user of the reference expects, checked without a GPU."""
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+REFERENCE_ENTRY_POINTS = [
+    "get_unique_id", "init_with_uid", "exchange", "nvshmem_register", "nvshmem_unregister", "all_reduce_create",
+    "all_reduce_run", "all_reduce_destroy", "init_custom_ar", "all_reduce", "reduce_scatter", "all_gather", "dispose",
+    "meta_size", "register_buffer", "get_graph_buffer_ipc_meta", "register_graph_buffers",
+    "allocate_shared_buffer_and_handle", "open_mem_handle", "free_shared_buffer",
+]
+
+
+def test_extension_imports_without_a_gpu_and_has_every_reference_entry_point():
+    import torch  # noqa: F401
+    import penny_cpp
+    missing = [n for n in REFERENCE_ENTRY_POINTS if not hasattr(penny_cpp, n)]
+    assert missing == []
+    assert penny_cpp.meta_size() > 0
+    uid = penny_cpp.get_unique_id()
+    assert isinstance(uid, bytearray) and len(uid) == 32 and uid != penny_cpp.get_unique_id()
+    # algorithm ids 0-3 keep the reference's numbering
+    assert (penny_cpp.ALGO_RING_STANDARD, penny_cpp.ALGO_RING_SIMPLE, penny_cpp.ALGO_ONESHOT,
+            penny_cpp.ALGO_TWOSHOT) == (0, 1, 2, 3)
+
+
+def test_reference_import_paths():
+    from penny.custom_all_reduce import CustomAllreduce, is_weak_contiguous
+    from penny.utils import bench_kineto, initialize_distributed  # noqa: F401
+    for name in ("capture", "register_graph_buffers", "should_custom_ar", "all_reduce", "custom_all_reduce",
+                 "reduce_scatter", "custom_reduce_scatter", "all_gather", "custom_all_gather", "close",
+                 "create_shared_buffer", "free_shared_buffer"):
+        assert hasattr(CustomAllreduce, name), name
+    assert CustomAllreduce._SUPPORTED_WORLD_SIZES == [2, 4, 6, 8]
+    import torch
+    t = torch.arange(12).reshape(3, 4)
+    assert is_weak_contiguous(t) and is_weak_contiguous(t[1:]) and not is_weak_contiguous(t[:, :2])
+
+
+def test_bootstrap_mesh_between_processes(tmp_path):
+    """The native unique-id bootstrap (Unix sockets + fd passing) needs no GPU: two
+    processes build the mesh; creating the heap then fails cleanly without CUDA."""
+    import subprocess
+    code = r'''
+import sys, torch
+sys.path.insert(0, %r)
+import penny_cpp
+uid, rank = bytes.fromhex(sys.argv[1]), int(sys.argv[2])
+try:
+    penny_cpp.comm_create(uid, rank, 2, 1 << 22, 0, False, 2000)
+    print("created")
+except RuntimeError as e:
+    print("error:", str(e)[:60])
+''' % ROOT
+    import penny_cpp
+    uid = bytes(penny_cpp.get_unique_id()).hex()
+    procs = [subprocess.Popen([sys.executable, "-c", code, uid, str(r)], stdout=subprocess.PIPE, text=True)
+             for r in range(2)]
+    outs = [p.communicate(timeout=120)[0] for p in procs]
+    # both ranks met in the bootstrap and then failed on the missing GPU, not on the rendezvous
+    for o in outs:
+        assert o.startswith("error:") and "bootstrap" not in o, outs
