@@ -14,6 +14,12 @@
 
 #include "decode_kernels.h"
 
+#include <stdio.h>
+
+#include <mutex>
+
+#include "decode_attention_noalloc.h"
+
 namespace penny {
 
 namespace {
@@ -455,3 +461,102 @@ cudaError_t launch_argmax(const void* logits, int rows, int cols, float* out_val
 }
 
 }  // namespace penny
+
+// ---------------------------------------------------------------------------
+// Allocation-free decode attention (see decode_attention_noalloc.h).
+// ---------------------------------------------------------------------------
+namespace {
+
+// Split-KV partials of the allocation-free entry point.  In host code this name
+// is only a handle for cudaGetSymbolAddress, never a pointer a kernel may use.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[PENNY_NOALLOC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mu;
+void* g_noalloc_ptr[kMaxDevices] = {};
+bool g_noalloc_attr[kMaxDevices][4] = {};
+
+int noalloc_fail(int code, char* err, size_t err_len, const char* what, const char* detail) {
+  if (err != nullptr && err_len > 0) snprintf(err, err_len, "%s%s%s", what, detail ? ": " : "", detail ? detail : "");
+  return code;
+}
+
+template <int G>
+cudaError_t noalloc_launch(const void* qkv, const void* kcache, const void* vcache, const int* positions,
+                           void* out, float* part_o, float* part_ml, int B, int Hq, int Hkv, int max_len,
+                           int splits, float scale, bool* attr_done, cudaStream_t stream) {
+  if (!*attr_done) {
+    cudaError_t rc = cudaFuncSetAttribute(penny::k_decode_attn<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          penny::kAttnSmem);
+    if (rc != cudaSuccess) return rc;
+    *attr_done = true;
+  }
+  dim3 grid(B, Hkv, splits);
+  penny::k_decode_attn<G><<<grid, penny::kAttnWarps * 32, penny::kAttnSmem, stream>>>(
+      (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, positions,
+      (__nv_bfloat16*)out, part_o, part_ml, Hq, Hkv, max_len, splits, scale);
+  cudaError_t rc = cudaGetLastError();
+  if (rc != cudaSuccess || splits == 1) return rc;
+  penny::k_attn_merge<<<dim3(B, Hq), 32, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, Hq, splits);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) int penny_decode_attention_noalloc(
+    const void* qkv, const void* kcache, const void* vcache, const int* positions, void* out, int B, int Hq,
+    int Hkv, int max_len, int splits, float scale, void* stream, char* err, size_t err_len) {
+  if (qkv == nullptr || kcache == nullptr || vcache == nullptr || positions == nullptr || out == nullptr)
+    return noalloc_fail(1, err, err_len, "penny_decode_attention_noalloc: null pointer argument", nullptr);
+  if (B < 1 || Hq < 1 || Hkv < 1 || Hq % Hkv != 0 || max_len < 1 || splits < 1 || splits > 64)
+    return noalloc_fail(1, err, err_len, "penny_decode_attention_noalloc: bad shape (need B, Hq, Hkv, max_len >= 1, "
+                        "Hq a multiple of Hkv, 1 <= splits <= 64)", nullptr);
+  const int G = Hq / Hkv;
+  if (G != 1 && G != 2 && G != 4 && G != 8)
+    return noalloc_fail(1, err, err_len, "penny_decode_attention_noalloc: Hq / Hkv must be 1, 2, 4 or 8", nullptr);
+  const size_t need = penny::decode_attn_workspace_bytes(B, Hq, splits);
+  if (need > (size_t)PENNY_NOALLOC_SCRATCH_BYTES) {
+    char detail[160];
+    snprintf(detail, sizeof(detail), "B * Hq * splits * 520 = %zu bytes needed, %u built in; lower `splits` or use "
+             "the workspace-taking entry point", need, (unsigned)PENNY_NOALLOC_SCRATCH_BYTES);
+    return noalloc_fail(2, err, err_len, "penny_decode_attention_noalloc: too large for the built-in scratch", detail);
+  }
+  int dev = 0;
+  cudaError_t rc = cudaGetDevice(&dev);
+  if (rc != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return noalloc_fail(3, err, err_len, "penny_decode_attention_noalloc: cudaGetDevice", cudaGetErrorString(rc));
+  void* scratch = nullptr;
+  bool* attr_done = nullptr;
+  {
+    // once per device, with that device current: the device address of the array
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (g_noalloc_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      rc = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+      if (rc != cudaSuccess || p == nullptr) {
+        (void)cudaGetLastError();
+        return noalloc_fail(3, err, err_len, "penny_decode_attention_noalloc: cudaGetSymbolAddress",
+                            cudaGetErrorString(rc));
+      }
+      g_noalloc_ptr[dev] = p;
+    }
+    scratch = g_noalloc_ptr[dev];
+    attr_done = &g_noalloc_attr[dev][G == 1 ? 0 : G == 2 ? 1 : G == 4 ? 2 : 3];
+  }
+  float* part_o = reinterpret_cast<float*>(scratch);
+  float* part_ml = part_o + (size_t)B * Hq * splits * penny::kD;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  switch (G) {
+    case 1: rc = noalloc_launch<1>(qkv, kcache, vcache, positions, out, part_o, part_ml, B, Hq, Hkv, max_len, splits, scale, attr_done, s); break;
+    case 2: rc = noalloc_launch<2>(qkv, kcache, vcache, positions, out, part_o, part_ml, B, Hq, Hkv, max_len, splits, scale, attr_done, s); break;
+    case 4: rc = noalloc_launch<4>(qkv, kcache, vcache, positions, out, part_o, part_ml, B, Hq, Hkv, max_len, splits, scale, attr_done, s); break;
+    default: rc = noalloc_launch<8>(qkv, kcache, vcache, positions, out, part_o, part_ml, B, Hq, Hkv, max_len, splits, scale, attr_done, s); break;
+  }
+  if (rc != cudaSuccess) {
+    (void)cudaGetLastError();
+    return noalloc_fail(3, err, err_len, "penny_decode_attention_noalloc: launch", cudaGetErrorString(rc));
+  }
+  if (err != nullptr && err_len > 0) err[0] = '\0';
+  return 0;
+}
+
