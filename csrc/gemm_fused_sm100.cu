@@ -12,8 +12,8 @@
 //     in fp32, write the output shard.
 //
 //   all-gather -> GEMM       (column-parallel layer: qkv, gate/up)
-//     a few "side" CTAs push the local A shard row block by row block into every
-//     peer's gathered-A buffer (local memory of the peer) and flag each block;
+//     the copy warps of every CTA push the local A shard, 32 rows at a time, into
+//     every peer's gathered-A buffer (local memory of the peer) and flag it;
 //     the GEMM CTAs walk the row blocks starting with the local shard and their
 //     TMA producer waits for a block's flag before loading it – from LOCAL
 //     memory: remote tiles are landed first, never fetched by TMA from a peer,
@@ -62,17 +62,14 @@ struct GemmRsPolicy : PolicyBase {
     s.half = scratch_half(scratch_off, scratch_bytes, s.seq);
     return s;
   }
-  __device__ __forceinline__ void store_row(const State& st, int row, int col, const uint32_t (&v)[16],
-                                            int, int) const {
+  __device__ __forceinline__ void store16(const State& st, int row, int col, const uint4& v, int,
+                                          int) const {
     const int owner = row / rows_per_shard;
     const int lrow = row - owner * rows_per_shard;
     char* dst = c.heap[owner] + st.half + (((size_t)c.rank * rows_per_shard + lrow) * N + col) * 2;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      V16 x;
-      x.w[0] = v[4 * i]; x.w[1] = v[4 * i + 1]; x.w[2] = v[4 * i + 2]; x.w[3] = v[4 * i + 3];
-      st16(dst + i * 16, x);
-    }
+    V16 x;
+    x.w[0] = v.x; x.w[1] = v.y; x.w[2] = v.z; x.w[3] = v.w;
+    st16(dst, x);
   }
   __device__ __forceinline__ void tile_end(const State& st, int m_blk, int n_blk) const {
     // all 128 epilogue threads have issued their stores; one of them publishes the tile
@@ -142,53 +139,60 @@ struct AgGemmPolicy : PolicyBase {
     s.half = scratch_half(scratch_off, scratch_bytes, s.seq);
     return s;
   }
-  // unit u = (peer offset d, row block rb): d = 0 (the local copy) first
-  __device__ __forceinline__ void side_work(const State& st, int cta, int ncta, uint32_t*) const {
-    const int units = c.world * tiles_per_shard;
+  // unit u = (peer offset d, row block rb, quarter qq of 32 rows): d = 0 (the
+  // local copy) first.  Run by the copy warps of every CTA, so the pushes share
+  // the SMs with the MMAs instead of taking SMs away from them.
+  static constexpr int kSub = 4;
+  static constexpr int kDeep = 8;  // 16-byte vectors in flight per thread
+  __device__ __forceinline__ void side_work(const State& st, int cta, int ncta, int tid, uint32_t*) const {
+    const int units = c.world * tiles_per_shard * kSub;
     const int vec_per_row = K / 8;
     for (int u = cta; u < units; u += ncta) {
-      const int d = u / tiles_per_shard, rb = u % tiles_per_shard;
+      const int d = u / (tiles_per_shard * kSub);
+      const int rb = (u / kSub) % tiles_per_shard, qq = u % kSub;
       const int p = (c.rank + d) % c.world;
-      const int rows = min(kBlockM, rows_per_shard - rb * kBlockM);
-      char* dst = c.heap[p] + st.half + ((size_t)(c.rank * rows_per_shard + rb * kBlockM) * K) * 2;
+      const int row0 = rb * kBlockM + qq * (kBlockM / kSub);
+      const int rows = max(0, min(kBlockM / kSub, rows_per_shard - row0));
+      char* dst = c.heap[p] + st.half + ((size_t)(c.rank * rows_per_shard + row0) * K) * 2;
       const int total = rows * vec_per_row;
-      for (int i0 = threadIdx.x; i0 < total; i0 += kBatch * blockDim.x) {
-        V16 x[kBatch];
+      for (int i0 = tid; i0 < total; i0 += kDeep * kCopyThreads) {
+        V16 x[kDeep];
 #pragma unroll
-        for (int k = 0; k < kBatch; ++k) {
-          const int i = i0 + k * blockDim.x;
+        for (int k = 0; k < kDeep; ++k) {
+          const int i = i0 + k * kCopyThreads;
           if (i < total) {
             const int r = i / vec_per_row, cv = i % vec_per_row;
-            x[k] = ld16(a_shard + (size_t)(rb * kBlockM + r) * lda + cv * 8);
+            x[k] = ld16(a_shard + (size_t)(row0 + r) * lda + cv * 8);
           }
         }
 #pragma unroll
-        for (int k = 0; k < kBatch; ++k) {
-          const int i = i0 + k * blockDim.x;
+        for (int k = 0; k < kDeep; ++k) {
+          const int i = i0 + k * kCopyThreads;
           if (i < total) st16(dst + (size_t)i * 16, x[k]);
         }
       }
-      __syncthreads();
-      if (threadIdx.x == 0) {
+      named_bar_sync(2, kCopyThreads);
+      if (tid == 0) {
         const int m_blk = c.rank * tiles_per_shard + rb;
-        st_release_sys(&pad_of(c, p)->flag[CH_FUSED][m_blk][c.rank], flag_value(st.seq, 1));
+        st_release_sys(&pad_of(c, p)->flag[CH_FUSED][m_blk * kSub + qq][c.rank], flag_value(st.seq, 1));
       }
     }
   }
   __device__ __forceinline__ bool wait_rows(const State& st, int m_blk, int) const {
     const int owner = m_blk / tiles_per_shard;
-    if (!wait_flag_ge(&pad_of(c, c.rank)->flag[CH_FUSED][m_blk][owner], flag_value(st.seq, 1), c,
-                      ST_TIMEOUT_TILE, owner, m_blk))
-      return false;
+    for (int qq = 0; qq < kSub; ++qq)
+      if (!wait_flag_ge(&pad_of(c, c.rank)->flag[CH_FUSED][m_blk * kSub + qq][owner], flag_value(st.seq, 1),
+                        c, ST_TIMEOUT_TILE, owner, m_blk))
+        return false;
     fence_proxy_async();  // the rows were written by another GPU; TMA reads them next
     return true;
   }
   __device__ __forceinline__ int a_row_offset(const State& st) const {
     return (int)(st.seq & 1ull) * (rows_per_shard * c.world);
   }
-  __device__ __forceinline__ void store_row(const State&, int row, int col, const uint32_t (&v)[16],
-                                            int M, int N) const {
-    store_row_local(out, ldc, row, col, v, M, N);
+  __device__ __forceinline__ void store16(const State&, int row, int col, const uint4& v, int M,
+                                          int N) const {
+    store16_local(out, ldc, row, col, v, M, N);
   }
   __device__ __forceinline__ void finish(const State& st) const {
     const Blk b{(int)blockIdx.x, nblocks, (int)blockDim.x};
@@ -240,7 +244,6 @@ cudaError_t launch_gemm_rs(const CommCtx& c, size_t scratch_off, size_t scratch_
   }
   const int grid = std::min(sm_count(), tiles_m * tiles_n);
   Policy pol;
-  pol.side_ctas = 0;
   pol.c = c;
   pol.scratch_off = scratch_off;
   pol.scratch_bytes = scratch_bytes;
@@ -266,15 +269,13 @@ cudaError_t launch_ag_gemm(const CommCtx& c, size_t scratch_off, size_t scratch_
   if (M % (W * kBlockM) != 0 || K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0 || N <= 0)
     return cudaErrorInvalidValue;
   const int tiles_m = M / kBlockM, tps = tiles_m / W;
-  if (tiles_m > kMaxBlocks || scratch_bytes != ag_gemm_scratch_bytes(M, K)) return cudaErrorInvalidValue;
+  if (tiles_m * AgGemmPolicy::kSub > kMaxBlocks || scratch_bytes != ag_gemm_scratch_bytes(M, K))
+    return cudaErrorInvalidValue;
   const int BN = (N >= 256) ? 256 : 128;
   const int tiles_n = (N + BN - 1) / BN;
-  const int sms = sm_count();
-  if (side_ctas <= 0) side_ctas = 16;
-  side_ctas = std::min(side_ctas, std::min(W * tps, sms / 2));
-  const int grid = std::min(sms, side_ctas + tiles_m * tiles_n);
+  (void)side_ctas;  // kept for API compatibility: the pushes are done by copy warps of every CTA
+  const int grid = std::min(sm_count(), std::max(tiles_m * tiles_n, 1));
   AgGemmPolicy pol;
-  pol.side_ctas = side_ctas;
   pol.c = c;
   pol.scratch_off = scratch_off;
   pol.scratch_bytes = scratch_bytes;

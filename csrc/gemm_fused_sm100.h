@@ -21,7 +21,7 @@ cudaError_t launch_gemm_rs(const CommCtx& c, size_t scratch_off, size_t scratch_
 
 // out[M, N] = gather(A shards)[M, K] * B[N, K]^T, a_shard = this rank's [M / world, K] rows.
 // scratch: a region dedicated to this (M, K) of exactly ag_gemm_scratch_bytes(M, K).
-// side_ctas: CTAs that push the shard to the peers instead of computing (0 = default).
+// side_ctas: ignored (the pushes are done by copy warps inside every CTA).
 cudaError_t launch_ag_gemm(const CommCtx& c, size_t scratch_off, size_t scratch_bytes,
                            const void* a_shard, const void* b, void* out, int M, int N, int K, int lda,
                            int ldb, int ldc, int side_ctas, uint32_t* error_word,

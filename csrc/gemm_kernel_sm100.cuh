@@ -15,7 +15,9 @@ namespace penny {
 namespace sm100 {
 
 constexpr int kBlockM = 128;
-constexpr int kGemmThreads = 192;  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr int kGemmThreads = 320;  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-9 copy
+constexpr int kCopyThreads = 128;
+constexpr int kStageRowBytes = 128;  // epilogue staging: 64 bf16 columns per row and pass
 
 enum GemmError : uint32_t {
   GEMM_OK = 0,
@@ -37,11 +39,12 @@ struct GemmShape {
 // replace State (what begin() returns and every hook receives) and any hook.
 struct PolicyBase {
   struct State {};
-  int side_ctas = 0;
   __device__ __forceinline__ State begin() const { return State{}; }
-  // all threads of a side CTA
+  // the 128 threads of the copy warps of CTA `cta` (tid in [0, 128)); they run
+  // next to the CTA's GEMM roles and may only synchronise among themselves
+  // (named barrier 2)
   template <class S>
-  __device__ __forceinline__ void side_work(const S&, int /*cta*/, int /*ncta*/, uint32_t*) const {}
+  __device__ __forceinline__ void side_work(const S&, int /*cta*/, int /*ncta*/, int /*tid*/, uint32_t*) const {}
   // the producer thread, before the first A tile of a row block
   template <class S>
   __device__ __forceinline__ bool wait_rows(const S&, int /*m_blk*/, int /*n_blk*/) const { return true; }
@@ -68,21 +71,21 @@ struct GemmKernel {
   static constexpr int kBBytes = BN * kBlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 2 * BN;  // two accumulators
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+  static constexpr int kEpiStageBytes = 4 * 32 * kStageRowBytes;  // 4 warps x 32 rows x 128 B
+  static constexpr int kSmemBytes =
+      kStages * kStageBytes + kEpiStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
-// 32 bf16 (packed in 16 words) of one C row, bounds-checked.
-__device__ __forceinline__ void store_row_local(__nv_bfloat16* c, int ldc, int row, int col,
-                                                const uint32_t (&v)[16], int M, int N) {
-  if (row >= M) return;
+// 8 bf16 (16 bytes) of one C row, bounds-checked.
+__device__ __forceinline__ void store16_local(__nv_bfloat16* c, int ldc, int row, int col, const uint4& v,
+                                              int M, int N) {
+  if (row >= M || col >= N) return;
   __nv_bfloat16* dst = c + (size_t)row * ldc + col;
-  if (col + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-      *reinterpret_cast<uint4*>(dst + i * 8) = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  if (col + 8 <= N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+    *reinterpret_cast<uint4*>(dst) = v;
   } else {
-    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(v);
-    for (int i = 0; i < 32 && col + i < N; ++i) dst[i] = e[i];
+    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+    for (int i = 0; i < 8 && col + i < N; ++i) dst[i] = e[i];
   }
 }
 
@@ -105,13 +108,8 @@ gemm_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const GemmShape s, const Policy pol, uint32_t* error_word) {
   using Cfg = GemmKernel<BN>;
   const typename Policy::State st = pol.begin();
-  if ((int)blockIdx.x < pol.side_ctas) {
-    pol.side_work(st, blockIdx.x, pol.side_ctas, error_word);
-    pol.finish(st);
-    return;
-  }
-  const int cta = (int)blockIdx.x - pol.side_ctas;
-  const int ncta = (int)gridDim.x - pol.side_ctas;
+  const int cta = (int)blockIdx.x;
+  const int ncta = (int)gridDim.x;
   constexpr int kStages = Cfg::kStages;
   extern __shared__ unsigned char smem_raw[];
   // tiles need 1024-byte alignment for the 128-byte swizzle
@@ -122,6 +120,7 @@ gemm_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   uint64_t* empty = bars + kStages;
   uint64_t* tmem_full = bars + 2 * kStages;
   uint64_t* tmem_empty = bars + 2 * kStages + 2;
+  unsigned char* epi_stage = tiles + kStages * Cfg::kStageBytes + 256;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
@@ -235,7 +234,8 @@ gemm_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         umma_commit(&tmem_full[ab]);  // accumulator complete
       }
     }
-  } else {
+  } else if (warp < 6) {
+    {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;  // the TMEM lane quarter this warp may read
     int it = 0;
@@ -250,16 +250,40 @@ gemm_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
       tc_fence_after_sync();
       pol.tile_begin(st, m_blk, n_blk);
-      const int row = m_blk * kBlockM + q * 32 + lane;
+      // 64 columns per pass: TMEM -> registers (thread = row) -> this warp's
+      // swizzled staging rows -> global, 8 lanes writing one contiguous 128-byte
+      // row segment (full lines also when the destination is a peer's memory)
+      unsigned char* stg = epi_stage + (warp - 2) * (32 * kStageRowBytes);
+      const int row0 = m_blk * kBlockM + q * 32;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + (uint32_t)(ab * BN + c * 32) + ((uint32_t)(q * 32) << 16), r);
+      for (int c = 0; c < BN / 64; ++c) {
+        uint32_t r0[32], r1[32];
+        const uint32_t taddr = tmem_base + (uint32_t)(ab * BN + c * 64) + ((uint32_t)(q * 32) << 16);
+        tmem_ld_32x32(taddr, r0);
+        tmem_ld_32x32(taddr + 32, r1);
         tmem_ld_wait();
-        uint32_t v[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = pack_bf16x2(r[2 * i], r[2 * i + 1]);
-        pol.store_row(st, row, n_blk * BN + c * 32, v, s.M, s.N);
+        for (int j = 0; j < 4; ++j) {
+          uint4 v;
+          v.x = pack_bf16x2(r0[8 * j], r0[8 * j + 1]);
+          v.y = pack_bf16x2(r0[8 * j + 2], r0[8 * j + 3]);
+          v.z = pack_bf16x2(r0[8 * j + 4], r0[8 * j + 5]);
+          v.w = pack_bf16x2(r0[8 * j + 6], r0[8 * j + 7]);
+          *reinterpret_cast<uint4*>(stg + lane * kStageRowBytes + ((j ^ (lane & 7)) << 4)) = v;
+          v.x = pack_bf16x2(r1[8 * j], r1[8 * j + 1]);
+          v.y = pack_bf16x2(r1[8 * j + 2], r1[8 * j + 3]);
+          v.z = pack_bf16x2(r1[8 * j + 4], r1[8 * j + 5]);
+          v.w = pack_bf16x2(r1[8 * j + 6], r1[8 * j + 7]);
+          *reinterpret_cast<uint4*>(stg + lane * kStageRowBytes + (((j + 4) ^ (lane & 7)) << 4)) = v;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int it2 = 0; it2 < 8; ++it2) {
+          const int rr = it2 * 4 + (lane >> 3), j = lane & 7;
+          const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * kStageRowBytes + ((j ^ (rr & 7)) << 4));
+          pol.store16(st, row0 + rr, n_blk * BN + c * 64 + j * 8, v, s.M, s.N);
+        }
+        __syncwarp();
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -267,6 +291,10 @@ gemm_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       pol.tile_end(st, m_blk, n_blk);
     }
     pol.after_tiles(st, cta, ncta, (int)threadIdx.x - 64, error_word);
+  }
+  } else {
+    // ---------------------------------------------------------------- copy warps
+    pol.side_work(st, cta, ncta, (int)threadIdx.x - 192, error_word);
   }
   // ------------------------------------------------------------------- teardown
   tc_fence_before_sync();

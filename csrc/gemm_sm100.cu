@@ -7,8 +7,11 @@
 //               K=16) into one of two TMEM accumulators; tcgen05.commit hands
 //               ring slots back to the producer and accumulators to the epilogue
 //   warps 2-5   epilogue: tcgen05.ld the finished accumulator (each warp its
-//               own 32-lane quarter), convert to bf16, store to global memory –
+//               own 32-lane quarter), convert to bf16, transpose through a small
+//               swizzled staging buffer and store full 128-byte row segments –
 //               overlapped with the MMAs of the next tile
+//   warps 6-9   copy warps: idle here; in the fused kernels they move operand
+//               shards between GPUs while the other warps compute
 // One CTA per SM; tiles are handed out round-robin with the M index fastest so
 // that CTAs working at the same time share a B tile in L2.
 //
@@ -75,9 +78,9 @@ cudaError_t make_tile_map(CUtensorMap* map, const void* base, uint64_t rows, uin
 struct StoreLocal : PolicyBase {
   __nv_bfloat16* c;
   int ldc;
-  __device__ __forceinline__ void store_row(const State&, int row, int col, const uint32_t (&v)[16],
-                                            int M, int N) const {
-    store_row_local(c, ldc, row, col, v, M, N);
+  __device__ __forceinline__ void store16(const State&, int row, int col, const uint4& v, int M,
+                                          int N) const {
+    store16_local(c, ldc, row, col, v, M, N);
   }
 };
 
