@@ -51,17 +51,51 @@ def parse():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    """Samples SM clocks and throttle reasons while a region runs.
+
+    Polls NVML from a thread every few milliseconds (a TP-8 timed region can be shorter than one nvidia-smi
+    period); falls back to an `nvidia-smi -lms` child when the NVML binding is missing. Read-only queries.
+    """
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    BITS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, uuid: str = None):
         self.gpu = gpu_index
+        self.uuid = uuid
         self.proc = None
         self.lines = []
+        self.nvml = None
+        self.sm, self.mx, self.reasons = [], None, set()
+        self._stop = threading.Event()
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        if self.uuid:
+            u = self.uuid if self.uuid.startswith("GPU-") else "GPU-" + self.uuid
+            try:
+                return pynvml, pynvml.nvmlDeviceGetHandleByUUID(u.encode())
+            except pynvml.NVMLError:
+                pass
+        return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.gpu)
+
+    def prepare(self):
+        """Opens NVML (tens of milliseconds) so that start() inside the timed region only spawns the thread."""
+        try:
+            self.nvml, self.handle = self._nvml_handle()
+            self.mx = float(self.nvml.nvmlDeviceGetMaxClockInfo(self.handle, self.nvml.NVML_CLOCK_SM))
+            self.nvml.nvmlDeviceGetClockInfo(self.handle, self.nvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nvml = None
+        return self
 
     def start(self):
+        if self.nvml is not None:
+            self.t = threading.Thread(target=self._poll, daemon=True)
+            self.t.start()
+            return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.Q}",
                                           "--format=csv,noheader,nounits", "-lms", "100"],
@@ -71,11 +105,36 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def _poll_once(self):
+        n = self.nvml
+        self.sm.append(float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)))
+        try:
+            mask = int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+        except Exception:
+            mask = 0
+        for bit, name in self.BITS.items():
+            if mask & bit:
+                self.reasons.add(name)
+
+    def _poll(self):
+        while True:
+            try:
+                self._poll_once()
+            except Exception:
+                return
+            if self._stop.wait(0.005):
+                return
+
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
     def stop(self):
+        if self.nvml is not None:
+            self._stop.set()
+            self.t.join(timeout=2)
+            return {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": self.mx,
+                    "reasons": sorted(self.reasons), "samples": len(self.sm), "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -98,7 +157,14 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "source": "nvidia-smi"}
+
+
+def _gpu_uuid(torch):
+    try:
+        return str(torch.cuda.get_device_properties(torch.cuda.current_device()).uuid)
+    except Exception:
+        return None
 
 
 def run_penny(args):
@@ -133,14 +199,14 @@ def run_penny(args):
     for _ in range(args.warmup):
         model.step_device()
     sync_all()
-    sampler = ClockSampler(torch.cuda.current_device())
-    sampler.start()
-    time.sleep(0.15)
+    sampler = ClockSampler(torch.cuda.current_device(), _gpu_uuid(torch)).prepare()
     sync_all()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for i in range(args.steps):
         model.step_device()
+        if i == 0:
+            sampler.start()  # samples only while the timed steps are in flight
     e1.record()
     sync_all()
     ms = e0.elapsed_time(e1)
@@ -333,14 +399,14 @@ def run_reference(args):
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    sampler = ClockSampler(torch.cuda.current_device())
-    sampler.start()
-    time.sleep(0.15)
+    sampler = ClockSampler(torch.cuda.current_device(), _gpu_uuid(torch)).prepare()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for i in range(args.steps):
         run_step()
+        if i == 0:
+            sampler.start()  # samples only while the timed steps are in flight
     e1.record()
     torch.cuda.synchronize()
     if world > 1:
