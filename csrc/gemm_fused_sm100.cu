@@ -19,6 +19,11 @@
 //     memory: remote tiles are landed first, never fetched by TMA from a peer,
 //     and no load uses cluster multicast.
 //
+// Both run on CTA pairs (cta_group::2, 256 x 256 tiles; gemm_kernel_pair_sm100.cuh)
+// when every rank's shard is a whole number of 256-row blocks and there is at
+// least one tile per pair, else on the single-CTA 128 x BN kernel; the policies
+// are the same for both.
+//
 // Both use the communicator's call sequence (scratch halves, flag values) like
 // every other collective, and every wait is bounded.  The reference has neither
 // (it has no GEMM at all); NCCL-based code runs the two steps back to back.
@@ -26,6 +31,7 @@
 
 #include "coll_args.h"
 #include "gemm_fused_sm100.h"
+#include "gemm_kernel_pair_sm100.cuh"
 #include "gemm_kernel_sm100.cuh"
 #include "gemm_sm100.h"
 
@@ -230,19 +236,28 @@ cudaError_t launch_gemm_rs(const CommCtx& c, size_t scratch_off, size_t scratch_
   const int tiles_m = M / kBlockM, tiles_n = N / BN, tps = tiles_m / W;
   if (tps * tiles_n > kMaxBlocks || scratch_bytes < gemm_rs_scratch_bytes(M, N, W))
     return cudaErrorInvalidValue;
+  using Policy = GemmRsPolicy<BN>;
+  const int sms = sm_count();
+  static int pairs = 0;
+  if (pairs == 0) {
+    cudaError_t rc0 = set_smem(gemm_persistent_pair<Policy>, PairGemmKernel::kSmemBytes);
+    if (rc0 != cudaSuccess) return rc0;
+    pairs = max_resident_pairs(reinterpret_cast<const void*>(gemm_persistent_pair<Policy>),
+                               PairGemmKernel::kSmemBytes, sms);
+  }
+  const bool pair = pair_kernel_enabled() && tps % 2 == 0 && (tiles_m / 2) * tiles_n >= pairs && K >= 1024;
   CUtensorMap ma, mb;
   cudaError_t rc = make_tile_map(&ma, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, kBlockM);
   if (rc != cudaSuccess) return rc;
-  rc = make_tile_map(&mb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN);
+  rc = make_tile_map(&mb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, pair ? BN / 2 : BN);
   if (rc != cudaSuccess) return rc;
-  using Policy = GemmRsPolicy<BN>;
   static bool attr = false;
   if (!attr) {
     rc = set_smem(gemm_persistent<BN, Policy>, GemmKernel<BN>::kSmemBytes);
     if (rc != cudaSuccess) return rc;
     attr = true;
   }
-  const int grid = std::min(sm_count(), tiles_m * tiles_n);
+  const int grid = pair ? 2 * std::min(pairs, (tiles_m / 2) * tiles_n) : std::min(sms, tiles_m * tiles_n);
   Policy pol;
   pol.c = c;
   pol.scratch_off = scratch_off;
@@ -256,8 +271,12 @@ cudaError_t launch_gemm_rs(const CommCtx& c, size_t scratch_off, size_t scratch_
   pol.nblocks = grid;
   // owners in the order rank+1, rank+2, ..., rank: local rows last
   GemmShape shape{M, N, K, tiles_m, tiles_n, ((c.rank + 1) % W) * tps, tiles_m * tiles_n, 0};
-  gemm_persistent<BN, Policy><<<grid, kGemmThreads, GemmKernel<BN>::kSmemBytes, stream>>>(
-      ma, mb, shape, pol, error_word);
+  if (pair)
+    gemm_persistent_pair<Policy><<<grid, kGemmThreads, PairGemmKernel::kSmemBytes, stream>>>(
+        ma, mb, shape, pol, error_word);
+  else
+    gemm_persistent<BN, Policy><<<grid, kGemmThreads, GemmKernel<BN>::kSmemBytes, stream>>>(
+        ma, mb, shape, pol, error_word);
   return cudaGetLastError();
 }
 
@@ -274,7 +293,18 @@ cudaError_t launch_ag_gemm(const CommCtx& c, size_t scratch_off, size_t scratch_
   const int BN = (N >= 256) ? 256 : 128;
   const int tiles_n = (N + BN - 1) / BN;
   (void)side_ctas;  // kept for API compatibility: the pushes are done by copy warps of every CTA
-  const int grid = std::min(sm_count(), std::max(tiles_m * tiles_n, 1));
+  const int sms = sm_count();
+  static int pairs = 0;
+  if (pairs == 0) {
+    cudaError_t rc0 = set_smem(gemm_persistent_pair<AgGemmPolicy>, PairGemmKernel::kSmemBytes);
+    if (rc0 != cudaSuccess) return rc0;
+    pairs = max_resident_pairs(reinterpret_cast<const void*>(gemm_persistent_pair<AgGemmPolicy>),
+                               PairGemmKernel::kSmemBytes, sms);
+  }
+  const bool pair = pair_kernel_enabled() && BN == 256 && tps % 2 == 0 && (tiles_m / 2) * tiles_n >= pairs &&
+                    K >= 1024;
+  const int grid = pair ? 2 * std::min(pairs, (tiles_m / 2) * tiles_n)
+                        : std::min(sms, std::max(tiles_m * tiles_n, 1));
   AgGemmPolicy pol;
   pol.c = c;
   pol.scratch_off = scratch_off;
@@ -296,10 +326,13 @@ cudaError_t launch_ag_gemm(const CommCtx& c, size_t scratch_off, size_t scratch_
   const char* afull = c.heap[c.rank] + scratch_off;
   cudaError_t rc = make_tile_map(&ma, afull, (uint64_t)2 * M, (uint64_t)K, (uint64_t)K, kBlockM);
   if (rc != cudaSuccess) return rc;
-  rc = make_tile_map(&mb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN);
+  rc = make_tile_map(&mb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, pair ? 128 : BN);
   if (rc != cudaSuccess) return rc;
   GemmShape shape{M, N, K, tiles_m, tiles_n, c.rank * tps, tiles_m * tiles_n, 0};
-  if (BN == 256) {
+  if (pair) {
+    gemm_persistent_pair<AgGemmPolicy><<<grid, kGemmThreads, PairGemmKernel::kSmemBytes, stream>>>(
+        ma, mb, shape, pol, error_word);
+  } else if (BN == 256) {
     static bool attr = false;
     if (!attr) {
       rc = set_smem(gemm_persistent<256, AgGemmPolicy>, GemmKernel<256>::kSmemBytes);

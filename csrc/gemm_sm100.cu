@@ -15,18 +15,24 @@
 // One CTA per SM; tiles are handed out round-robin with the M index fastest so
 // that CTAs working at the same time share a B tile in L2.
 //
+// Large problems run the CTA-pair variant instead (gemm_kernel_pair_sm100.cuh:
+// cta_group::2, 256 x 256 tiles over two SMs, a third less shared-memory fill
+// traffic per FLOP); block_n = 512 selects it explicitly.
+//
 // The same main loop is the body of the fused kernels (GEMM -> reduce-scatter,
 // all-gather -> GEMM): they differ in where the epilogue writes and in what the
-// producer waits for.  Those variants live in gemm_rs_sm100.cu / ag_gemm_sm100.cu
-// and instantiate gemm_persistent<> with their own policies.
+// producer waits for.  Those variants live in gemm_fused_sm100.cu and
+// instantiate gemm_persistent<> / gemm_persistent_pair<> with their own policies.
 #include "gemm_sm100.h"
 
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <stdexcept>
 #include <string>
 
+#include "gemm_kernel_pair_sm100.cuh"
 #include "gemm_kernel_sm100.cuh"
 
 namespace penny {
@@ -111,6 +117,64 @@ cudaError_t launch_gemm_bn(const void* a, const void* b, void* c, int M, int N, 
   return cudaGetLastError();
 }
 
+// How many CTA pairs of `kernel` the device can hold at once (the persistent grid).
+int max_resident_pairs(const void* kernel, int smem_bytes, int sms) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)sms & ~1u, 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = (size_t)smem_bytes;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
+    (void)cudaGetLastError();
+    n = sms / 2 - 2;  // conservative: a GPC with an odd SM count strands one SM
+  }
+  return std::min(n, sms / 2);
+}
+
+bool pair_kernel_enabled() {
+  static const bool on = []() {
+    const char* e = getenv("PENNY_GEMM_PAIR");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
+
+// 256 x 256 tiles on CTA pairs (cta_group::2).
+cudaError_t launch_gemm_pair(const void* a, const void* b, void* c, int M, int N, int K, int lda,
+                             int ldb, int ldc, int sms, uint32_t* error_word, cudaStream_t stream) {
+  CUtensorMap ma, mb;
+  cudaError_t rc = make_tile_map(&ma, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, kBlockM);
+  if (rc != cudaSuccess) return rc;
+  rc = make_tile_map(&mb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, PairGemmKernel::kTileN / 2);
+  if (rc != cudaSuccess) return rc;
+  static int pairs = 0;
+  if (pairs == 0) {
+    rc = cudaFuncSetAttribute(gemm_persistent_pair<StoreLocal>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize, PairGemmKernel::kSmemBytes);
+    if (rc != cudaSuccess) return rc;
+    pairs = max_resident_pairs(reinterpret_cast<const void*>(gemm_persistent_pair<StoreLocal>),
+                               PairGemmKernel::kSmemBytes, sms);
+  }
+  const int tiles_m = (M + kBlockM - 1) / kBlockM;
+  const int tiles_n = (N + PairGemmKernel::kTileN - 1) / PairGemmKernel::kTileN;
+  const int ptiles = ((tiles_m + 1) / 2) * tiles_n;
+  const int grid = 2 * std::min(pairs, ptiles);
+  GemmShape shape{M, N, K, tiles_m, tiles_n, 0, tiles_m * tiles_n, 1};
+  StoreLocal ep;
+  ep.c = reinterpret_cast<__nv_bfloat16*>(c);
+  ep.ldc = ldc;
+  gemm_persistent_pair<StoreLocal><<<grid, kGemmThreads, PairGemmKernel::kSmemBytes, stream>>>(
+      ma, mb, shape, ep, error_word);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, int lda,
                              int ldb, int ldc, int block_n, uint32_t* error_word,
                              cudaStream_t stream) {
@@ -119,7 +183,13 @@ cudaError_t launch_gemm_bf16(const void* a, const void* b, void* c, int M, int N
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (block_n == 0) block_n = (N >= 256 && (long long)((M + 127) / 128) * ((N + 255) / 256) >= sms / 2) ? 256 : 128;
+  if (block_n == 0) {
+    const long long t256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
+    // CTA pairs once every pair has a tile and K is long enough to hide the epilogue
+    if (pair_kernel_enabled() && N >= 256 && t256 / 2 >= sms / 2 && K >= 1024) block_n = 512;
+    else block_n = (N >= 256 && t256 >= sms / 2) ? 256 : 128;
+  }
+  if (block_n == 512) return launch_gemm_pair(a, b, c, M, N, K, lda, ldb, ldc, sms, error_word, stream);
   if (block_n == 256) return launch_gemm_bn<256>(a, b, c, M, N, K, lda, ldb, ldc, sms, error_word, stream);
   if (block_n == 128) return launch_gemm_bn<128>(a, b, c, M, N, K, lda, ldb, ldc, sms, error_word, stream);
   return cudaErrorInvalidValue;

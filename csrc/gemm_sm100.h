@@ -15,11 +15,18 @@ cudaError_t make_tile_map(CUtensorMap* map, const void* base, uint64_t rows, uin
 
 // C[M, N] = A[M, K] * B[N, K]^T, bf16, row-major with leading dimensions lda /
 // ldb / ldc (elements).  K, lda, ldb multiples of 8.  block_n: 0 (choose), 128 or
-// 256.  error_word: device word that receives a GemmError code if a pipeline
+// 256 (one CTA per 128 x block_n tile), or 512 = 256 x 256 tiles computed by CTA
+// pairs (cta_group::2).  error_word: device word that receives a GemmError code if a pipeline
 // wait runs out (stays 0 otherwise).
 cudaError_t launch_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, int lda,
                              int ldb, int ldc, int block_n, uint32_t* error_word,
                              cudaStream_t stream);
+
+// Number of CTA pairs (clusters of two) of `kernel` that can be resident at once
+// with `smem_bytes` of dynamic shared memory: the grid of the pair kernels.
+int max_resident_pairs(const void* kernel, int smem_bytes, int sms);
+// False when PENNY_GEMM_PAIR=0 forces the single-CTA kernels everywhere.
+bool pair_kernel_enabled();
 
 }  // namespace sm100
 }  // namespace penny

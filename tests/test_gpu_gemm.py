@@ -9,7 +9,7 @@ def ref(a, b):
     return a.float() @ b.float().t()
 
 
-@pytest.mark.parametrize("block_n", [128, 256])
+@pytest.mark.parametrize("block_n", [128, 256, 512])  # 512: 256 x 256 tiles on CTA pairs (cta_group::2)
 @pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (300, 520, 264), (1, 4096, 4096),
                                    (64, 1792, 4096), (4096, 768, 4096), (1000, 3584, 1024)])
 def test_gemm_matches_fp32(shape, block_n):
@@ -65,5 +65,29 @@ def test_fused_gemm_kernels_single_rank():
             out3 = comm.all_gather_gemm(a, w2, side_ctas=3)
             assert ops.gemm_error() == 0
             torch.testing.assert_close(out3.float(), ref(a, w2), atol=0.15, rtol=1.6e-2)
+    finally:
+        comm.close()
+
+
+def test_fused_gemm_kernels_single_rank_cta_pairs():
+    """The same two fused kernels on shapes large enough (one 256 x 256 tile per
+    CTA pair, K >= 1024) that their launchers choose the cta_group::2 kernel."""
+    from penny_b200._ext import ops
+    from penny_b200.parallel.comm import Communicator
+    comm = Communicator.emulated(1, heap_bytes=512 << 20, timeout_ms=2000)
+    try:
+        M, N, K = 4096, 1280, 1024
+        a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+        w = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+        want = ref(a, w)
+        for it in range(3):  # both scratch halves
+            out = comm.gemm_reduce_scatter(a, w)
+            assert ops.gemm_error() == 0
+            comm.check()
+            torch.testing.assert_close(out.float(), want, atol=0.3, rtol=1.6e-2)
+            out2 = comm.all_gather_gemm(a, w)
+            assert ops.gemm_error() == 0
+            comm.check()
+            torch.testing.assert_close(out2.float(), want, atol=0.3, rtol=1.6e-2)
     finally:
         comm.close()
