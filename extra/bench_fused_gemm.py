@@ -33,14 +33,15 @@ def peaks():
     return tf, link, src
 
 
-def main():
-    ap = argparse.ArgumentParser()
+def add_args(ap):
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--side-ctas", type=int, default=0)
-    args = ap.parse_args()
-    rank, world, comm = initialize_distributed(heap_bytes=2 << 30)
+
+
+def run(rank, world, comm, args):
+    """All four linears on an initialised communicator (heap >= 2 GiB); rank 0 prints one JSON line per op."""
     tf, link, src = peaks()
     M, H, F, D = args.tokens, 4096, 14336, 128
     qkv_n = (32 + 2 * 8) * D // world
@@ -103,6 +104,14 @@ def main():
                               "bound": "compute" if flops / (tf * 1e6) > wire / (link * 1e3) else "nvlink"}), flush=True)
     assert ops.gemm_error() == 0
     comm.check()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    add_args(ap)
+    args = ap.parse_args()
+    rank, world, comm = initialize_distributed(heap_bytes=2 << 30)
+    run(rank, world, comm, args)
     shutdown()
 
 

@@ -20,14 +20,15 @@ from penny_b200.models.moe_ep import MoeConfig, MoeEPLayer  # noqa: E402
 from penny_b200.utils import bench_device, initialize_distributed, shutdown  # noqa: E402
 
 
-def main():
-    ap = argparse.ArgumentParser()
+def add_args(ap):
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--ffn", type=int, default=14336)
-    args = ap.parse_args()
-    rank, world, comm = initialize_distributed(heap_bytes=3 << 30)
+
+
+def run(rank, world, comm, args):
+    """One layer, both backends, on an initialised communicator (heap >= 3 GiB); rank 0 prints one JSON line."""
     cfg = MoeConfig.mixtral_8x7b()
     cfg.ffn = args.ffn
     if cfg.experts % world:
@@ -52,6 +53,14 @@ def main():
                           "nccl_all_to_all_us": round(t_n, 1), "speedup": round(t_n / t_p, 3),
                           "wire_mb_per_rank_each_way": round(rows * cfg.hidden * 2 * (world - 1) / world / 1e6, 1)}),
               flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    add_args(ap)
+    args = ap.parse_args()
+    rank, world, comm = initialize_distributed(heap_bytes=3 << 30)
+    run(rank, world, comm, args)
     shutdown()
 
 
