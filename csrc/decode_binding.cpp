@@ -34,6 +34,12 @@ void bind_decode(py::module_& m) {
                           (int)qkv.size(0), (int)Hq, (int)Hkv, (int)D, (int)kcache.size(2), (float)theta, cur()),
        "rope_append");
   });
+  m.def("rope_rows", [](at::Tensor qkv, int64_t Hq, int64_t Hkv, int64_t D, int64_t pos0, double theta) {
+    need(bf16_cuda(qkv) && qkv.dim() == 2 && qkv.size(1) == (Hq + 2 * Hkv) * D, "rope_rows expects [T, (Hq + 2 Hkv) D] bf16");
+    const at::cuda::OptionalCUDAGuard guard(qkv.device());
+    ck(launch_rope_rows(qkv.data_ptr(), (int)qkv.size(0), (int)Hq, (int)Hkv, (int)D, (int)pos0, (float)theta, cur()),
+       "rope_rows");
+  });
   m.def("decode_attn_workspace_bytes", [](int64_t B, int64_t Hq, int64_t splits) {
     return (int64_t)decode_attn_workspace_bytes((int)B, (int)Hq, (int)splits);
   });

@@ -63,6 +63,23 @@ __global__ void k_rope_append(__nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __
   }
 }
 
+// RoPE for a prefill: row t of qkv is token pos0 + t of one sequence.
+// grid = (T, ceil((Hq + Hkv) / 4)), block = (D / 2, 4): four heads per block.
+__global__ void k_rope_rows(__nv_bfloat16* __restrict__ qkv, int Hq, int Hkv, int D, int pos0, float theta) {
+  const int t = blockIdx.x;
+  const int h = blockIdx.y * blockDim.y + threadIdx.y;
+  if (h >= Hq + Hkv) return;
+  const int i = threadIdx.x;
+  const int half = D / 2;
+  __nv_bfloat16* x = qkv + (size_t)t * (Hq + 2 * Hkv) * D + (size_t)h * D;
+  const float inv_freq = __powf(theta, -2.0f * (float)i / (float)D);
+  float s, c;
+  __sincosf((float)(pos0 + t) * inv_freq, &s, &c);
+  const float a = bf2f(x[i]), bb = bf2f(x[i + half]);
+  x[i] = __float2bfloat16_rn(a * c - bb * s);
+  x[i + half] = __float2bfloat16_rn(bb * c + a * s);
+}
+
 // ---------------------------------------------------------------------------
 // Decode attention, head_dim 128, grouped queries, on tensor cores.
 //
@@ -400,6 +417,14 @@ cudaError_t launch_rope_append(void* qkv, void* kcache, void* vcache, const int*
   k_rope_append<<<grid, D / 2, 0, stream>>>((__nv_bfloat16*)qkv, (__nv_bfloat16*)kcache,
                                             (__nv_bfloat16*)vcache, positions, Hq, Hkv, D, max_len,
                                             theta);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rope_rows(void* qkv, int T, int Hq, int Hkv, int D, int pos0, float theta,
+                             cudaStream_t stream) {
+  if (D % 2 != 0 || D / 2 > 256 || T <= 0) return cudaErrorInvalidValue;
+  dim3 grid(T, (Hq + Hkv + 3) / 4), block(D / 2, 4);
+  k_rope_rows<<<grid, block, 0, stream>>>((__nv_bfloat16*)qkv, Hq, Hkv, D, pos0, theta);
   return cudaGetLastError();
 }
 

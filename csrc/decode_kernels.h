@@ -11,6 +11,11 @@ cudaError_t launch_rope_append(void* qkv, void* kcache, void* vcache, const int*
                                int Hq, int Hkv, int D, int max_len, float theta,
                                cudaStream_t stream);
 
+// Prefill form: rotates the q and k heads of every row of qkv [T, (Hq + 2*Hkv) * D] in
+// place at position pos0 + row (one sequence of T tokens); v is left alone.
+cudaError_t launch_rope_rows(void* qkv, int T, int Hq, int Hkv, int D, int pos0, float theta,
+                             cudaStream_t stream);
+
 // Scratch the split-KV attention needs: per (row, head, split) an unnormalised
 // fp32 output row plus (max, sum).
 size_t decode_attn_workspace_bytes(int B, int Hq, int splits);

@@ -270,7 +270,7 @@ cudaError_t launch_gemm_rs(const CommCtx& c, size_t scratch_off, size_t scratch_
   pol.tiles_n = tiles_n;
   pol.nblocks = grid;
   // owners in the order rank+1, rank+2, ..., rank: local rows last
-  GemmShape shape{M, N, K, tiles_m, tiles_n, ((c.rank + 1) % W) * tps, tiles_m * tiles_n, 0};
+  GemmShape shape{M, N, K, tiles_m, tiles_n, ((c.rank + 1) % W) * tps, tiles_m * tiles_n, 0, 0};
   if (pair)
     gemm_persistent_pair<Policy><<<grid, kGemmThreads, PairGemmKernel::kSmemBytes, stream>>>(
         ma, mb, shape, pol, error_word);
@@ -328,7 +328,7 @@ cudaError_t launch_ag_gemm(const CommCtx& c, size_t scratch_off, size_t scratch_
   if (rc != cudaSuccess) return rc;
   rc = make_tile_map(&mb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, pair ? 128 : BN);
   if (rc != cudaSuccess) return rc;
-  GemmShape shape{M, N, K, tiles_m, tiles_n, c.rank * tps, tiles_m * tiles_n, 0};
+  GemmShape shape{M, N, K, tiles_m, tiles_n, c.rank * tps, tiles_m * tiles_n, 0, 0};
   if (pair) {
     gemm_persistent_pair<AgGemmPolicy><<<grid, kGemmThreads, PairGemmKernel::kSmemBytes, stream>>>(
         ma, mb, shape, pol, error_word);

@@ -88,13 +88,7 @@ gemm_persistent_pair(const __grid_constant__ CUtensorMap map_a, const __grid_con
 
   auto decode = [&](int tile, int& m_blk, int& n_blk) {
     int pm_raw;
-    if (s.m_fastest) {
-      pm_raw = tile % tiles_pm;
-      n_blk = tile / tiles_pm;
-    } else {
-      pm_raw = tile / s.tiles_n;
-      n_blk = tile % s.tiles_n;
-    }
+    tile_order(s, tile, tiles_pm, s.group_m >> 1, pm_raw, n_blk);
     m_blk = 2 * ((pm_raw + (s.m_rot >> 1)) % tiles_pm) + (int)r;
   };
   auto fail = [&](uint32_t code) {

@@ -33,7 +33,32 @@ struct GemmShape {
   int m_rot;      // row-block rotation: tile row r works on block (r + m_rot) % tiles_m
   int num_tiles;
   int m_fastest;  // 1: consecutive tiles walk down M (share a B tile); 0: walk along N
+  // > 0 (with m_fastest = 1): tiles are handed out in bands of `group_m` row
+  // blocks, M fastest inside a band, so that the tiles in flight at one time
+  // cover a square-ish patch of C and A's band stays in L2 from wave to wave
+  int group_m;
 };
+
+// Tile index -> (row-block index before rotation, column block) in the order
+// described by GemmShape, for `rows_m` row blocks (row-block pairs in the
+// CTA-pair kernel) and group height `gm` in the same unit.
+__device__ __forceinline__ void tile_order(const GemmShape& s, int tile, int rows_m, int gm, int& m_raw,
+                                           int& n_blk) {
+  if (!s.m_fastest) {
+    m_raw = tile / s.tiles_n;
+    n_blk = tile % s.tiles_n;
+  } else if (gm <= 0 || gm >= rows_m) {
+    m_raw = tile % rows_m;
+    n_blk = tile / rows_m;
+  } else {
+    const int per_group = gm * s.tiles_n;
+    const int g = tile / per_group, in_g = tile - g * per_group;
+    const int first = g * gm;
+    const int h = min(gm, rows_m - first);
+    m_raw = first + in_g % h;
+    n_blk = in_g / h;
+  }
+}
 
 // The policy of the plain GEMM; also documents the interface.  A policy may
 // replace State (what begin() returns and every hook receives) and any hook.
@@ -148,13 +173,7 @@ gemm_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   auto decode = [&](int tile, int& m_blk, int& n_blk) {
     int m_raw;
-    if (s.m_fastest) {
-      m_raw = tile % s.tiles_m;
-      n_blk = tile / s.tiles_m;
-    } else {
-      m_raw = tile / s.tiles_n;
-      n_blk = tile % s.tiles_n;
-    }
+    tile_order(s, tile, s.tiles_m, s.group_m, m_raw, n_blk);
     m_blk = (m_raw + s.m_rot) % s.tiles_m;
   };
   auto fail = [&](uint32_t code) {

@@ -108,7 +108,7 @@ cudaError_t launch_gemm_bn(const void* a, const void* b, void* c, int M, int N, 
   }
   const int tiles_m = (M + kBlockM - 1) / kBlockM, tiles_n = (N + BN - 1) / BN;
   const int grid = std::min(sms, tiles_m * tiles_n);
-  GemmShape shape{M, N, K, tiles_m, tiles_n, 0, tiles_m * tiles_n, 1};
+  GemmShape shape{M, N, K, tiles_m, tiles_n, 0, tiles_m * tiles_n, 1, 16};
   StoreLocal ep;
   ep.c = reinterpret_cast<__nv_bfloat16*>(c);
   ep.ldc = ldc;
@@ -166,7 +166,7 @@ cudaError_t launch_gemm_pair(const void* a, const void* b, void* c, int M, int N
   const int tiles_n = (N + PairGemmKernel::kTileN - 1) / PairGemmKernel::kTileN;
   const int ptiles = ((tiles_m + 1) / 2) * tiles_n;
   const int grid = 2 * std::min(pairs, ptiles);
-  GemmShape shape{M, N, K, tiles_m, tiles_n, 0, tiles_m * tiles_n, 1};
+  GemmShape shape{M, N, K, tiles_m, tiles_n, 0, tiles_m * tiles_n, 1, 16};
   StoreLocal ep;
   ep.c = reinterpret_cast<__nv_bfloat16*>(c);
   ep.ldc = ldc;

@@ -10,7 +10,9 @@ measurements themselves):
   2. the Mixtral-shaped expert-parallel layer of extra/bench_moe_ep.py against
      NCCL all_to_all_single,
   3. all-to-all and pairwise exchange at three sizes against NCCL
-     (all_to_all_single, batch_isend_irecv).
+     (all_to_all_single, batch_isend_irecv),
+  4. the sequence-parallel prefill stack of extra/bench_sp_prefill.py (fused
+     linears against cuBLAS + NCCL).
 Rank 0 prints one JSON line per measurement.  Device time everywhere: CUDA
 events, L2 flushed between calls, ranks aligned, median, max over ranks.
 """
@@ -26,6 +28,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import bench_fused_gemm  # noqa: E402
 import bench_moe_ep  # noqa: E402
+import bench_sp_prefill  # noqa: E402
 from penny_b200.utils import bench_device, initialize_distributed, shutdown  # noqa: E402
 
 
@@ -77,7 +80,8 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--heap-gib", type=float, default=4.0)
-    ap.add_argument("--skip", nargs="*", default=[], choices=["gemm", "moe", "exchange"])
+    ap.add_argument("--skip", nargs="*", default=[], choices=["gemm", "moe", "exchange", "sp"])
+    ap.add_argument("--sp-layers", type=int, default=8, help="layers of the sequence-parallel prefill stack")
     args = ap.parse_args()
     rank, world, comm = initialize_distributed(heap_bytes=int(args.heap_gib * (1 << 30)))
     if "gemm" not in args.skip:
@@ -88,6 +92,9 @@ def main():
                                                                warmup=args.warmup, ffn=14336))
     if "exchange" not in args.skip:
         run_exchange(rank, world, comm, [64 << 10, 1 << 20, 16 << 20], args.warmup, args.iters)
+    if "sp" not in args.skip:
+        bench_sp_prefill.run(rank, world, comm, argparse.Namespace(tokens=args.tokens, layers=args.sp_layers,
+                                                                   iters=5, warmup=2))
     comm.check()
     shutdown()
 

@@ -3,6 +3,7 @@ profiler capture on ONE GPU (a few launches, well under a GB on the device
 except where DRAM figures need inputs larger than L2).
 
     python extra/profile_kernels.py gemm        # tcgen05 GEMM 4096^3, 3 launches
+    python extra/profile_kernels.py gemm_pair   # the same on CTA pairs (cta_group::2), 8192^3, 3 launches
     python extra/profile_kernels.py attention   # decode attention, batch 64 x 8 KV heads x 2048
     python extra/profile_kernels.py fused       # all-reduce+residual+RMSNorm, 8 emulated ranks
     python extra/profile_kernels.py allreduce   # two-shot / LL all-reduce, 8 emulated ranks
@@ -44,6 +45,14 @@ def main():
         t = timed(lambda: ops.gemm_bf16(a, b, c, 256))
         assert ops.gemm_error() == 0
         print(f"gemm_bf16 {M}x{N}x{K}: {t:.1f} us, {2 * M * N * K / t / 1e6:.1f} TFLOP/s")
+    elif what == "gemm_pair":
+        M = N = K = 8192
+        a = torch.randn(M, K, device="cuda").bfloat16()
+        b = torch.randn(N, K, device="cuda").bfloat16()
+        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        t = timed(lambda: ops.gemm_bf16(a, b, c, 512), n=2)
+        assert ops.gemm_error() == 0
+        print(f"gemm_bf16 (CTA pairs) {M}x{N}x{K}: {t:.1f} us, {2 * M * N * K / t / 1e6:.1f} TFLOP/s")
     elif what == "attention":
         B, Hq, Hkv, D, L = 64, 32, 8, 128, 2048
         qkv = torch.randn(B, (Hq + 2 * Hkv) * D, device="cuda").bfloat16()

@@ -225,6 +225,28 @@ def main():
             assert torch.all(chosen >= want.max(-1).values - 0.1 * want.std()), (backend, proto)
     check("tp_decode", run_tp_decode)
 
+    # ---- sequence-parallel prefill (fused GEMM + collective in every linear) vs fp32 on one GPU ----
+    def run_sp_prefill():
+        from penny_b200.models.llama_sp import LlamaSPPrefill
+        from penny_b200.models.llama_tp import LlamaConfig
+        cfg = LlamaConfig.tiny()
+        if cfg.kv_heads % world:
+            cfg.kv_heads, cfg.heads = world, 4 * world
+        T, L = 256 * world, 2
+        g = torch.Generator(device="cuda").manual_seed(77)
+        x = torch.randn(T, cfg.hidden, device="cuda", generator=g).bfloat16()       # same on all ranks
+        want = LlamaSPPrefill.reference_forward(cfg, x, L, seed=3)
+        rows = T // world
+        for backend in ("penny", "nccl"):
+            m = LlamaSPPrefill(cfg, comm=comm, rank=rank, world=world, tokens=T, layers=L, backend=backend, seed=3)
+            for _ in range(2):  # both scratch halves
+                got = m.forward(x[rank * rows:(rank + 1) * rows]).float()
+                comm.check()
+                ref = want[rank * rows:(rank + 1) * rows]
+                rel = ((got - ref).norm() / ref.norm()).item()
+                assert rel < 3e-2, (backend, rel)
+    check("sp_prefill", run_sp_prefill)
+
     # ---- the reference-style module API on the process-wide communicator ----
     import penny_cpp
     from penny_b200.utils import global_communicator

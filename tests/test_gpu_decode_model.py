@@ -87,3 +87,42 @@ def test_decoder_matches_fp32_reference(use_graph):
     # public host API
     host = m.step(torch.zeros(6, dtype=torch.int64))
     assert host.shape == (6,) and host.device.type == "cpu"
+
+
+def test_sp_prefill_single_rank_matches_fp32():
+    """Sequence-parallel prefill block with a world of one: every linear runs the
+    fused tcgen05 kernel (heap slots, flags, gathered-buffer TMA), attention,
+    RoPE, norms and silu*mul run as in the multi-rank case."""
+    from penny_b200.models.llama_sp import LlamaSPPrefill
+    from penny_b200.models.llama_tp import LlamaConfig
+    from penny_b200.parallel.comm import Communicator
+    cfg = LlamaConfig.tiny()
+    T, L = 512, 2
+    x = torch.randn(T, cfg.hidden, device="cuda", generator=torch.Generator(device="cuda").manual_seed(5)).bfloat16()
+    want = LlamaSPPrefill.reference_forward(cfg, x, L, seed=1)
+    comm = Communicator.emulated(1, heap_bytes=256 << 20, timeout_ms=2000)
+    try:
+        for backend in ("penny", "nccl"):
+            m = LlamaSPPrefill(cfg, comm=comm, tokens=T, layers=L, backend=backend, seed=1)
+            got = m.forward(x).float()
+            comm.check()
+            rel = ((got - want).norm() / want.norm()).item()
+            assert rel < 3e-2, (backend, rel)
+    finally:
+        comm.close()
+
+
+def test_rope_rows_matches_reference():
+    from penny_b200._ext import ops
+    T, Hq, Hkv, D, theta = 37, 4, 2, 128, 500000.0
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda").bfloat16()
+    want = qkv.float().clone().view(T, Hq + 2 * Hkv, D)
+    half = D // 2
+    inv = theta ** (-2.0 * torch.arange(half, device="cuda", dtype=torch.float32) / D)
+    ang = (torch.arange(T, device="cuda", dtype=torch.float32) + 11)[:, None] * inv[None]
+    c, s_ = ang.cos()[:, None], ang.sin()[:, None]
+    a, b = want[:, :Hq + Hkv, :half].clone(), want[:, :Hq + Hkv, half:].clone()
+    want[:, :Hq + Hkv, :half] = a * c - b * s_
+    want[:, :Hq + Hkv, half:] = b * c + a * s_
+    ops.rope_rows(qkv, Hq, Hkv, D, 11, theta)
+    torch.testing.assert_close(qkv.float().view(T, Hq + 2 * Hkv, D), want, atol=3e-2, rtol=2e-2)
