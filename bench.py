@@ -32,7 +32,7 @@ import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
-BASELINE_TOKS = None  # the reference publishes no numbers
+PUBLISHED_TOKS = None  # the reference publishes no tokens/s figure for this config
 
 
 def parse():

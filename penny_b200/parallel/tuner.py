@@ -4,8 +4,8 @@
 algorithm); `Tuner.from_sweep` keeps, for every size, the fastest algorithm, and
 `Tuner.pick` looks a size up (nearest measured size at or above it).  The table
 is cached as JSON (`PENNY_TUNER_CACHE`, default ~/.cache/penny_b200/tuner.json)
-and a built-in default – taken from the sweeps recorded in this repository's
-BASELINE.md – is used when no cache exists.  Overrides: `PENNY_ALGO=<name>`
+and a built-in default – taken from sweeps of this script on an 8 x B200
+NVSwitch box – is used when no cache exists.  Overrides: `PENNY_ALGO=<name>`
 forces one algorithm; `VLLM_CUSTOM_ALLREDUCE_ALGO` keeps its meaning for the
 drop-in CustomAllreduce (1stage|oneshot|2stage|twoshot), as in the reference
 (csrc/custom_all_reduce.cuh:803-818), whose own choice is a fixed size threshold
