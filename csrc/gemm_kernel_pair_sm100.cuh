@@ -83,14 +83,9 @@ gemm_persistent_pair(const __grid_constant__ CUtensorMap map_a, const __grid_con
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
   const int num_kb = (s.K + kBlockK - 1) / kBlockK;
-  const int tiles_pm = (s.tiles_m + 1) >> 1;
-  const int num_ptiles = tiles_pm * s.tiles_n;
+  const int num_ptiles = pair_tile_count(s);
 
-  auto decode = [&](int tile, int& m_blk, int& n_blk) {
-    int pm_raw;
-    tile_order(s, tile, tiles_pm, s.group_m >> 1, pm_raw, n_blk);
-    m_blk = 2 * ((pm_raw + (s.m_rot >> 1)) % tiles_pm) + (int)r;
-  };
+  auto decode = [&](int tile, int& m_blk, int& n_blk) { decode_pair_tile(s, tile, (int)r, m_blk, n_blk); };
   auto fail = [&](uint32_t code) {
     *s_abort = 1;
     st_cluster_u32(map_to_cta(smem_u32(const_cast<int*>(s_abort)), r ^ 1u), 1u);

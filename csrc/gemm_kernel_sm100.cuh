@@ -10,6 +10,7 @@
 // See gemm_sm100.cu for the role layout.
 #pragma once
 #include "gemm_sm100.cuh"
+#include "gemm_tile_order.h"
 
 namespace penny {
 namespace sm100 {
@@ -26,39 +27,6 @@ enum GemmError : uint32_t {
   GEMM_ERR_EPILOGUE_WAIT = 103,
   GEMM_ERR_GATE_WAIT = 104,
 };
-
-struct GemmShape {
-  int M, N, K;
-  int tiles_m, tiles_n;
-  int m_rot;      // row-block rotation: tile row r works on block (r + m_rot) % tiles_m
-  int num_tiles;
-  int m_fastest;  // 1: consecutive tiles walk down M (share a B tile); 0: walk along N
-  // > 0 (with m_fastest = 1): tiles are handed out in bands of `group_m` row
-  // blocks, M fastest inside a band, so that the tiles in flight at one time
-  // cover a square-ish patch of C and A's band stays in L2 from wave to wave
-  int group_m;
-};
-
-// Tile index -> (row-block index before rotation, column block) in the order
-// described by GemmShape, for `rows_m` row blocks (row-block pairs in the
-// CTA-pair kernel) and group height `gm` in the same unit.
-__device__ __forceinline__ void tile_order(const GemmShape& s, int tile, int rows_m, int gm, int& m_raw,
-                                           int& n_blk) {
-  if (!s.m_fastest) {
-    m_raw = tile / s.tiles_n;
-    n_blk = tile % s.tiles_n;
-  } else if (gm <= 0 || gm >= rows_m) {
-    m_raw = tile % rows_m;
-    n_blk = tile / rows_m;
-  } else {
-    const int per_group = gm * s.tiles_n;
-    const int g = tile / per_group, in_g = tile - g * per_group;
-    const int first = g * gm;
-    const int h = min(gm, rows_m - first);
-    m_raw = first + in_g % h;
-    n_blk = in_g / h;
-  }
-}
 
 // The policy of the plain GEMM; also documents the interface.  A policy may
 // replace State (what begin() returns and every hook receives) and any hook.
@@ -171,11 +139,7 @@ gemm_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const uint32_t tmem_base = *tmem_holder;
   const int num_kb = (s.K + kBlockK - 1) / kBlockK;
 
-  auto decode = [&](int tile, int& m_blk, int& n_blk) {
-    int m_raw;
-    tile_order(s, tile, s.tiles_m, s.group_m, m_raw, n_blk);
-    m_blk = (m_raw + s.m_rot) % s.tiles_m;
-  };
+  auto decode = [&](int tile, int& m_blk, int& n_blk) { decode_tile(s, tile, m_blk, n_blk); };
   auto fail = [&](uint32_t code) {
     *s_abort = 1;
     atomicCAS(error_word, 0u, code);

@@ -23,6 +23,7 @@
 #include <vector>
 
 #include "../algos.h"
+#include "../gemm_tile_order.h"
 #include "../all_reduce_oneshot.cuh"
 #include "../all_reduce_ring.cuh"
 #include "../all_reduce_tree.cuh"
@@ -319,4 +320,17 @@ void penny_sched_split_span(unsigned long long V, int parts, int i, unsigned lon
   *e = s.end;
 }
 int penny_status_words() { return penny::kStatusWords; }
+// Tile -> (row block, column block) of the persistent GEMM kernels; pair_rank < 0
+// selects the single-CTA kernel, 0 / 1 the CTA of a pair.  Returns the number of
+// tiles (pair tiles) of the grid.
+int penny_gemm_tile_at(int tiles_m, int tiles_n, int m_rot, int m_fastest, int group_m, int pair_rank,
+                       int tile, int* m_blk, int* n_blk) {
+  penny::sm100::GemmShape s{0, 0, 0, tiles_m, tiles_n, m_rot, tiles_m * tiles_n, m_fastest, group_m};
+  if (pair_rank < 0) {
+    penny::sm100::decode_tile(s, tile, *m_blk, *n_blk);
+    return s.num_tiles;
+  }
+  penny::sm100::decode_pair_tile(s, tile, pair_rank, *m_blk, *n_blk);
+  return penny::sm100::pair_tile_count(s);
+}
 }

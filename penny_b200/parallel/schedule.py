@@ -88,3 +88,15 @@ def split_span(total: int, parts: int, i: int) -> Tuple[int, int]:
     e = ctypes.c_ulonglong(0)
     lib.penny_sched_split_span(ctypes.c_ulonglong(total), parts, i, ctypes.byref(b), ctypes.byref(e))
     return b.value, e.value
+
+
+def gemm_tile_at(tiles_m: int, tiles_n: int, tile: int, m_rot: int = 0, m_fastest: int = 1, group_m: int = 0,
+                 pair_rank: int = -1) -> Tuple[int, int, int]:
+    """(row block, column block, tiles in the grid) that the persistent tcgen05 GEMM
+    gives to step `tile`: the single-CTA kernel for pair_rank < 0, CTA 0 / 1 of a
+    CTA pair otherwise.  Same code as the device kernels (csrc/gemm_tile_order.h)."""
+    lib = sim_lib()
+    m, n = ctypes.c_int(0), ctypes.c_int(0)
+    total = lib.penny_gemm_tile_at(tiles_m, tiles_n, m_rot, m_fastest, group_m, pair_rank, tile,
+                                   ctypes.byref(m), ctypes.byref(n))
+    return m.value, n.value, total

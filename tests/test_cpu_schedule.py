@@ -86,3 +86,40 @@ def test_split_span_partitions():
         assert spans[0][0] == 0 and spans[-1][1] == total
         for (b0, e0), (b1, e1) in zip(spans, spans[1:]):
             assert e0 == b1 and b0 <= e0
+
+
+@pytest.mark.parametrize("tiles_m,tiles_n", [(1, 1), (7, 3), (32, 16), (33, 5), (64, 32), (16, 1)])
+@pytest.mark.parametrize("m_fastest,group_m", [(0, 0), (1, 0), (1, 16), (1, 6)])
+def test_gemm_tile_order_covers_every_tile_once(tiles_m, tiles_n, m_fastest, group_m):
+    """The persistent GEMM's tile order is a bijection onto the tile grid, for
+    the single-CTA kernel and (as row-block pairs) for the CTA-pair kernel."""
+    from penny_b200.parallel import schedule
+    for m_rot in (0, 2 * (tiles_m // 3)):
+        total = schedule.gemm_tile_at(tiles_m, tiles_n, 0, m_rot, m_fastest, group_m)[2]
+        assert total == tiles_m * tiles_n
+        seen = {schedule.gemm_tile_at(tiles_m, tiles_n, t, m_rot, m_fastest, group_m)[:2] for t in range(total)}
+        assert seen == {(m, n) for m in range(tiles_m) for n in range(tiles_n)}
+        # pairs: CTA 0 and CTA 1 of a pair get vertically adjacent row blocks of the same column block
+        ptotal = schedule.gemm_tile_at(tiles_m, tiles_n, 0, m_rot, m_fastest, group_m, pair_rank=0)[2]
+        assert ptotal == ((tiles_m + 1) // 2) * tiles_n
+        got = set()
+        for t in range(ptotal):
+            m0, n0, _ = schedule.gemm_tile_at(tiles_m, tiles_n, t, m_rot, m_fastest, group_m, pair_rank=0)
+            m1, n1, _ = schedule.gemm_tile_at(tiles_m, tiles_n, t, m_rot, m_fastest, group_m, pair_rank=1)
+            assert m0 % 2 == 0 and m1 == m0 + 1 and n0 == n1
+            got.add((m0, n0))
+            if m1 < tiles_m:
+                got.add((m1, n1))
+            else:
+                assert tiles_m % 2 == 1 and m1 == tiles_m   # the odd last row block has no partner
+        assert got == {(m, n) for m in range(tiles_m) for n in range(tiles_n)}
+
+
+def test_gemm_tile_order_band_is_squareish():
+    """With bands of 16 row blocks, the 148 tiles in flight touch 16 row blocks and
+    about 10 column blocks instead of all 64 row blocks and 3 columns."""
+    from penny_b200.parallel import schedule
+    wave = [schedule.gemm_tile_at(64, 32, t, group_m=16)[:2] for t in range(148)]
+    assert len({m for m, _ in wave}) == 16 and len({n for _, n in wave}) == 10
+    flat = [schedule.gemm_tile_at(64, 32, t, group_m=0)[:2] for t in range(148)]
+    assert len({m for m, _ in flat}) == 64 and len({n for _, n in flat}) == 3
