@@ -41,6 +41,8 @@ void bind_gemm(py::module_& m) {
         (int)out.stride(0), (int)block_n, penny_gemm_error_word(), at::cuda::getCurrentCUDAStream().stream());
     TORCH_CHECK(rc == cudaSuccess, "gemm_bf16: ", cudaGetErrorString(rc));
   }, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("block_n") = 0);
+  m.def("gemm_set_split_tail", [](int64_t on) { penny::sm100::set_split_tail((int)on); }, py::arg("on"),
+        "1 / 0: split (or not) the ragged last wave of the CTA-pair GEMM along K; -1: PENNY_GEMM_SPLIT_TAIL decides");
   // Synchronises; returns and clears the error code of the GEMM kernels (0 = fine).
   m.def("gemm_error", []() {
     at::Tensor& w = error_word();

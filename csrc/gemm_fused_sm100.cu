@@ -290,10 +290,15 @@ cudaError_t launch_ag_gemm(const CommCtx& c, size_t scratch_off, size_t scratch_
   const int tiles_m = M / kBlockM, tps = tiles_m / W;
   if (tiles_m * AgGemmPolicy::kSub > kMaxBlocks || scratch_bytes != ag_gemm_scratch_bytes(M, K))
     return cudaErrorInvalidValue;
-  const int BN = (N >= 256) ? 256 : 128;
+  const int sms = sm_count();
+  int BN = (N >= 256) ? 256 : 128;
+  if (N >= 192) {
+    // 128 x 192 tiles when they fill the SMs better (e.g. N = 768: 128 tiles instead of 96)
+    auto waves = [&](int bn) { return (double)((tiles_m * ((N + bn - 1) / bn) + sms - 1) / sms); };
+    if (waves(192) * 0.75 * 1.20 < waves(256) * 1.12) BN = 192;
+  }
   const int tiles_n = (N + BN - 1) / BN;
   (void)side_ctas;  // kept for API compatibility: the pushes are done by copy warps of every CTA
-  const int sms = sm_count();
   static int pairs = 0;
   if (pairs == 0) {
     cudaError_t rc0 = set_smem(gemm_persistent_pair<AgGemmPolicy>, PairGemmKernel::kSmemBytes);
@@ -331,6 +336,15 @@ cudaError_t launch_ag_gemm(const CommCtx& c, size_t scratch_off, size_t scratch_
   GemmShape shape{M, N, K, tiles_m, tiles_n, c.rank * tps, tiles_m * tiles_n, 0, 0};
   if (pair) {
     gemm_persistent_pair<AgGemmPolicy><<<grid, kGemmThreads, PairGemmKernel::kSmemBytes, stream>>>(
+        ma, mb, shape, pol, error_word);
+  } else if (BN == 192) {
+    static bool attr = false;
+    if (!attr) {
+      rc = set_smem(gemm_persistent<192, AgGemmPolicy>, GemmKernel<192>::kSmemBytes);
+      if (rc != cudaSuccess) return rc;
+      attr = true;
+    }
+    gemm_persistent<192, AgGemmPolicy><<<grid, kGemmThreads, GemmKernel<192>::kSmemBytes, stream>>>(
         ma, mb, shape, pol, error_word);
   } else if (BN == 256) {
     static bool attr = false;

@@ -17,6 +17,12 @@
 //     epilogue warps of both CTAs.
 //   * Each CTA drains its own 128 accumulator rows exactly like the single-CTA
 //     kernel, through the same Policy hooks, so the fused variants plug in.
+//   * Ragged last wave: when GemmShape::split_s > 1 the leftover tiles are cut
+//     along K into split_s ranges computed by different pairs at the same time
+//     (gemm_tile_order.h: plan_split_tail / pair_work).  Each range's fp32
+//     accumulator goes to a workspace; the CTA that arrives last on the tile's
+//     counter adds the ranges in order and runs the normal epilogue, then
+//     resets the counter for the next launch.
 // Every wait is bounded; a failure in one CTA also raises the abort flag of the
 // other.  Both CTAs pass a cluster barrier before the pair's TMEM is freed.
 #pragma once
@@ -59,6 +65,7 @@ gemm_persistent_pair(const __grid_constant__ CUtensorMap map_a, const __grid_con
   unsigned char* epi_stage = tiles + kStages * Cfg::kStageBytes + 256;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  volatile int* s_last = reinterpret_cast<volatile int*>(tmem_holder + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -83,7 +90,6 @@ gemm_persistent_pair(const __grid_constant__ CUtensorMap map_a, const __grid_con
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
   const int num_kb = (s.K + kBlockK - 1) / kBlockK;
-  const int num_ptiles = pair_tile_count(s);
 
   auto decode = [&](int tile, int& m_blk, int& n_blk) { decode_pair_tile(s, tile, (int)r, m_blk, n_blk); };
   auto fail = [&](uint32_t code) {
@@ -99,15 +105,16 @@ gemm_persistent_pair(const __grid_constant__ CUtensorMap map_a, const __grid_con
       uint32_t phase = 0;
       const int a_row0 = pol.a_row_offset(st);
       bool ok = true;
-      for (int tile = pair; tile < num_ptiles && !*s_abort; tile += npairs) {
+      PairWork w;
+      for (int it = 0; pair_work(s, num_kb, pair, npairs, it, w) && !*s_abort; ++it) {
         int m_blk, n_blk;
-        decode(tile, m_blk, n_blk);
+        decode(w.tile, m_blk, n_blk);
         if (m_blk < s.tiles_m && !pol.wait_rows(st, m_blk, n_blk)) {
           fail(GEMM_ERR_GATE_WAIT);
           ok = false;
           break;
         }
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait_abortable(&empty[stage], phase ^ 1u, s_abort)) {
             ok = false;
             break;
@@ -143,14 +150,14 @@ gemm_persistent_pair(const __grid_constant__ CUtensorMap map_a, const __grid_con
       constexpr uint32_t idesc = make_idesc_bf16(2 * kBlockM, BN);
       int stage = 0;
       uint32_t phase = 0;
-      int it = 0;
-      for (int tile = pair; tile < num_ptiles && !*s_abort; tile += npairs, ++it) {
+      PairWork w;
+      for (int it = 0; pair_work(s, num_kb, pair, npairs, it, w) && !*s_abort; ++it) {
         const int ab = it & 1;
         const uint32_t ab_phase = (uint32_t)(it >> 1) & 1u;
         bool ok = mbar_wait_abortable(&tmem_empty[ab], ab_phase ^ 1u, s_abort);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + (uint32_t)(ab * BN);
-        for (int kb = 0; ok && kb < num_kb; ++kb) {
+        for (int kb = w.kb0; ok && kb < w.kb1; ++kb) {
           if (!mbar_wait_abortable(&full[stage], phase, s_abort)) {
             ok = false;
             break;
@@ -161,7 +168,8 @@ gemm_persistent_pair(const __grid_constant__ CUtensorMap map_a, const __grid_con
           const uint64_t db = make_smem_desc(sa + Cfg::kABytes);
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; ++k)
-            umma_bf16_pair(d_tmem, advance_desc_k(da, k), advance_desc_k(db, k), idesc, (kb | k) != 0);
+            umma_bf16_pair(d_tmem, advance_desc_k(da, k), advance_desc_k(db, k), idesc,
+                           (kb != w.kb0) || k != 0);
           umma_commit_pair(&empty[stage], (uint16_t)3);  // frees the slot in both CTAs
           if (++stage == kStages) {
             stage = 0;
@@ -178,10 +186,37 @@ gemm_persistent_pair(const __grid_constant__ CUtensorMap map_a, const __grid_con
   } else if (warp < 6) {
     // ---------------------------------------- epilogue (own 128 rows, in each CTA)
     const int q = warp & 3;
-    int it = 0;
-    for (int tile = pair; tile < num_ptiles && !*s_abort; tile += npairs, ++it) {
+    unsigned char* stg = epi_stage + (warp - 2) * (32 * kStageRowBytes);
+    // 64 columns of this warp's 32 rows (fp32 bit patterns, thread = row) ->
+    // bf16 -> swizzled staging rows -> 128-byte row segments through the policy
+    auto emit = [&](int c, const uint32_t (&r0)[32], const uint32_t (&r1)[32], int row0, int n_blk) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 v;
+        v.x = pack_bf16x2(r0[8 * j], r0[8 * j + 1]);
+        v.y = pack_bf16x2(r0[8 * j + 2], r0[8 * j + 3]);
+        v.z = pack_bf16x2(r0[8 * j + 4], r0[8 * j + 5]);
+        v.w = pack_bf16x2(r0[8 * j + 6], r0[8 * j + 7]);
+        *reinterpret_cast<uint4*>(stg + lane * kStageRowBytes + ((j ^ (lane & 7)) << 4)) = v;
+        v.x = pack_bf16x2(r1[8 * j], r1[8 * j + 1]);
+        v.y = pack_bf16x2(r1[8 * j + 2], r1[8 * j + 3]);
+        v.z = pack_bf16x2(r1[8 * j + 4], r1[8 * j + 5]);
+        v.w = pack_bf16x2(r1[8 * j + 6], r1[8 * j + 7]);
+        *reinterpret_cast<uint4*>(stg + lane * kStageRowBytes + (((j + 4) ^ (lane & 7)) << 4)) = v;
+      }
+      __syncwarp();
+#pragma unroll
+      for (int it2 = 0; it2 < 8; ++it2) {
+        const int rr = it2 * 4 + (lane >> 3), j = lane & 7;
+        const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * kStageRowBytes + ((j ^ (rr & 7)) << 4));
+        pol.store16(st, row0 + rr, n_blk * BN + c * 64 + j * 8, v, s.M, s.N);
+      }
+      __syncwarp();
+    };
+    PairWork w;
+    for (int it = 0; pair_work(s, num_kb, pair, npairs, it, w) && !*s_abort; ++it) {
       int m_blk, n_blk;
-      decode(tile, m_blk, n_blk);
+      decode(w.tile, m_blk, n_blk);
       const int ab = it & 1;
       const uint32_t ab_phase = (uint32_t)(it >> 1) & 1u;
       if (!mbar_wait_abortable(&tmem_full[ab], ab_phase, s_abort)) {
@@ -190,43 +225,90 @@ gemm_persistent_pair(const __grid_constant__ CUtensorMap map_a, const __grid_con
       }
       tc_fence_after_sync();
       const bool live = m_blk < s.tiles_m;  // an odd last row block has no partner rows
-      if (live) pol.tile_begin(st, m_blk, n_blk);
-      unsigned char* stg = epi_stage + (warp - 2) * (32 * kStageRowBytes);
+      const bool split = s.split_s > 1 && w.tile >= s.split_first;
       const int row0 = m_blk * kBlockM + q * 32;
+      const uint32_t tacc = tmem_base + (uint32_t)(ab * BN) + ((uint32_t)(q * 32) << 16);
+      if (!split) {
+        if (live) pol.tile_begin(st, m_blk, n_blk);
+#pragma unroll 1
+        for (int c = 0; live && c < BN / 64; ++c) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(tacc + c * 64, r0);
+          tmem_ld_32x32(tacc + c * 64 + 32, r1);
+          tmem_ld_wait();
+          emit(c, r0, r1, row0, n_blk);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[ab]), 0u));
+        if (live) pol.tile_end(st, m_blk, n_blk);
+        continue;
+      }
+      // ---- one K range of a split tile: park the fp32 partial, the last one in adds them up
+      const int tail = w.tile - s.split_first;
+      // partial of (range, CTA): [64 vectors of 4 columns][128 rows] float4, so that the
+      // 32 rows of a warp are 512 contiguous bytes in every load and store
+      const int row_in_cta = q * 32 + lane;
+      auto part = [&](int seg) {
+        return reinterpret_cast<float4*>(s.split_ws) +
+               (size_t)((tail * s.split_s + seg) * 2 + (int)r) * (kBlockM * BN / 4) + row_in_cta;
+      };
 #pragma unroll 1
       for (int c = 0; live && c < BN / 64; ++c) {
         uint32_t r0[32], r1[32];
-        const uint32_t taddr = tmem_base + (uint32_t)(ab * BN + c * 64) + ((uint32_t)(q * 32) << 16);
-        tmem_ld_32x32(taddr, r0);
-        tmem_ld_32x32(taddr + 32, r1);
+        tmem_ld_32x32(tacc + c * 64, r0);
+        tmem_ld_32x32(tacc + c * 64 + 32, r1);
         tmem_ld_wait();
+        float4* dst = part(w.seg) + (size_t)(c * 16) * kBlockM;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 v;
-          v.x = pack_bf16x2(r0[8 * j], r0[8 * j + 1]);
-          v.y = pack_bf16x2(r0[8 * j + 2], r0[8 * j + 3]);
-          v.z = pack_bf16x2(r0[8 * j + 4], r0[8 * j + 5]);
-          v.w = pack_bf16x2(r0[8 * j + 6], r0[8 * j + 7]);
-          *reinterpret_cast<uint4*>(stg + lane * kStageRowBytes + ((j ^ (lane & 7)) << 4)) = v;
-          v.x = pack_bf16x2(r1[8 * j], r1[8 * j + 1]);
-          v.y = pack_bf16x2(r1[8 * j + 2], r1[8 * j + 3]);
-          v.z = pack_bf16x2(r1[8 * j + 4], r1[8 * j + 5]);
-          v.w = pack_bf16x2(r1[8 * j + 6], r1[8 * j + 7]);
-          *reinterpret_cast<uint4*>(stg + lane * kStageRowBytes + (((j + 4) ^ (lane & 7)) << 4)) = v;
+        for (int j = 0; j < 8; ++j) {
+          dst[(size_t)j * kBlockM] = make_float4(__uint_as_float(r0[4 * j]), __uint_as_float(r0[4 * j + 1]),
+                                                 __uint_as_float(r0[4 * j + 2]), __uint_as_float(r0[4 * j + 3]));
+          dst[(size_t)(8 + j) * kBlockM] = make_float4(__uint_as_float(r1[4 * j]), __uint_as_float(r1[4 * j + 1]),
+                                                       __uint_as_float(r1[4 * j + 2]), __uint_as_float(r1[4 * j + 3]));
         }
-        __syncwarp();
-#pragma unroll
-        for (int it2 = 0; it2 < 8; ++it2) {
-          const int rr = it2 * 4 + (lane >> 3), j = lane & 7;
-          const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * kStageRowBytes + ((j ^ (rr & 7)) << 4));
-          pol.store16(st, row0 + rr, n_blk * BN + c * 64 + j * 8, v, s.M, s.N);
-        }
-        __syncwarp();
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[ab]), 0u));
-      if (live) pol.tile_end(st, m_blk, n_blk);
+      if (!live) continue;  // the same for every range of this tile and CTA: no counter traffic
+      __threadfence();
+      named_bar_sync(1, 128);
+      if (threadIdx.x == 64) {
+        unsigned* cnt = s.split_counters + tail * 2 + (int)r;
+        const unsigned old = atomicAdd(cnt, 1u);
+        const int last = old == (unsigned)(s.split_s - 1);
+        if (last) *cnt = 0u;  // every range has arrived: ready for the next launch
+        *s_last = last;
+      }
+      named_bar_sync(1, 128);
+      if (!*s_last) continue;
+      __threadfence();
+      pol.tile_begin(st, m_blk, n_blk);
+#pragma unroll 1
+      for (int c = 0; c < BN / 64; ++c) {
+        float f0[32], f1[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f0[j] = f1[j] = 0.f;
+        for (int seg = 0; seg < s.split_s; ++seg) {  // fixed order: the sum does not depend on who is last
+          const float4* src = part(seg) + (size_t)(c * 16) * kBlockM;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 x = __ldcg(src + (size_t)j * kBlockM), y = __ldcg(src + (size_t)(8 + j) * kBlockM);
+            f0[4 * j] += x.x; f0[4 * j + 1] += x.y; f0[4 * j + 2] += x.z; f0[4 * j + 3] += x.w;
+            f1[4 * j] += y.x; f1[4 * j + 1] += y.y; f1[4 * j + 2] += y.z; f1[4 * j + 3] += y.w;
+          }
+        }
+        uint32_t r0[32], r1[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          r0[j] = __float_as_uint(f0[j]);
+          r1[j] = __float_as_uint(f1[j]);
+        }
+        emit(c, r0, r1, row0, n_blk);
+      }
+      pol.tile_end(st, m_blk, n_blk);
+      named_bar_sync(1, 128);  // s_last is rewritten by the next split tile only after all have read it
     }
     pol.after_tiles(st, cta, ncta, (int)threadIdx.x - 64, error_word);
   } else {

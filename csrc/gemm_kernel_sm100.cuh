@@ -59,11 +59,11 @@ struct PolicyBase {
 
 template <int BN>
 struct GemmKernel {
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 192 ? 5 : 6);
   static constexpr int kABytes = kBlockM * kBlockK * 2;
   static constexpr int kBBytes = BN * kBlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kTmemCols = 2 * BN;  // two accumulators
+  static constexpr int kTmemCols = (BN == 192) ? 512 : 2 * BN;  // two accumulators, a power of two
   static constexpr int kEpiStageBytes = 4 * 32 * kStageRowBytes;  // 4 warps x 32 rows x 128 B
   static constexpr int kSmemBytes =
       kStages * kStageBytes + kEpiStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;

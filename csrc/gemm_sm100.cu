@@ -27,7 +27,9 @@
 
 #include <cuda.h>
 
+#include <atomic>
 #include <cstdlib>
+#include <map>
 #include <mutex>
 #include <stdexcept>
 #include <string>
@@ -138,6 +140,20 @@ int max_resident_pairs(const void* kernel, int smem_bytes, int sms) {
   return std::min(n, sms / 2);
 }
 
+namespace {
+std::atomic<int> g_split_tail{-1};  // -1: take PENNY_GEMM_SPLIT_TAIL (default off)
+}
+void set_split_tail(int on) { g_split_tail.store(on < 0 ? -1 : (on != 0)); }
+bool split_tail_enabled() {
+  const int v = g_split_tail.load();
+  if (v >= 0) return v != 0;
+  static const bool on = []() {
+    const char* e = getenv("PENNY_GEMM_SPLIT_TAIL");
+    return e != nullptr && e[0] == '1';
+  }();
+  return on;
+}
+
 bool pair_kernel_enabled() {
   static const bool on = []() {
     const char* e = getenv("PENNY_GEMM_PAIR");
@@ -146,7 +162,45 @@ bool pair_kernel_enabled() {
   return on;
 }
 
-// 256 x 256 tiles on CTA pairs (cta_group::2).
+namespace {
+// fp32 partial tiles + arrival counters of the split last wave: one per
+// (device, stream), so that launches on different streams never share it.
+struct SplitScratch {
+  float* ws = nullptr;
+  unsigned* counters = nullptr;
+};
+constexpr int kMaxSplit = 4;
+
+SplitScratch* split_scratch(int dev, cudaStream_t stream, int pairs) {
+  static std::mutex mu;
+  static std::map<std::pair<int, cudaStream_t>, SplitScratch> table;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = table.find({dev, stream});
+  if (it != table.end()) return &it->second;
+  // never allocate while the stream is being captured: the caller falls back to unsplit tiles
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  SplitScratch sc;
+  const size_t ws_bytes = (size_t)pairs * 2 * kBlockM * PairGemmKernel::kTileN * sizeof(float);
+  if (cudaMalloc(&sc.ws, ws_bytes) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  if (cudaMalloc(&sc.counters, (size_t)pairs * 2 * sizeof(unsigned)) != cudaSuccess ||
+      cudaMemset(sc.counters, 0, (size_t)pairs * 2 * sizeof(unsigned)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    cudaFree(sc.ws);
+    return nullptr;
+  }
+  return &(table[{dev, stream}] = sc);
+}
+}  // namespace
+
+// 256 x 256 tiles on CTA pairs (cta_group::2).  A ragged last wave is split along
+// K over the idle pairs (at most kMaxSplit ranges per tile; gemm_tile_order.h).
 cudaError_t launch_gemm_pair(const void* a, const void* b, void* c, int M, int N, int K, int lda,
                              int ldb, int ldc, int sms, uint32_t* error_word, cudaStream_t stream) {
   CUtensorMap ma, mb;
@@ -165,14 +219,57 @@ cudaError_t launch_gemm_pair(const void* a, const void* b, void* c, int M, int N
   const int tiles_m = (M + kBlockM - 1) / kBlockM;
   const int tiles_n = (N + PairGemmKernel::kTileN - 1) / PairGemmKernel::kTileN;
   const int ptiles = ((tiles_m + 1) / 2) * tiles_n;
-  const int grid = 2 * std::min(pairs, ptiles);
   GemmShape shape{M, N, K, tiles_m, tiles_n, 0, tiles_m * tiles_n, 1, 16};
+  int npairs = std::min(pairs, ptiles);
+  plan_split_tail(shape, pairs, (K + kBlockK - 1) / kBlockK, split_tail_enabled() ? kMaxSplit : 1);
+  if (shape.split_s > 1) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    SplitScratch* sc = split_scratch(dev, stream, pairs);
+    if (sc != nullptr) {
+      shape.split_ws = sc->ws;
+      shape.split_counters = sc->counters;
+      npairs = pairs;  // the plan assumes the full grid
+    } else {
+      shape.split_s = 1;
+      shape.split_first = ptiles;
+    }
+  }
   StoreLocal ep;
   ep.c = reinterpret_cast<__nv_bfloat16*>(c);
   ep.ldc = ldc;
-  gemm_persistent_pair<StoreLocal><<<grid, kGemmThreads, PairGemmKernel::kSmemBytes, stream>>>(
+  gemm_persistent_pair<StoreLocal><<<2 * npairs, kGemmThreads, PairGemmKernel::kSmemBytes, stream>>>(
       ma, mb, shape, ep, error_word);
   return cudaGetLastError();
+}
+
+// Estimated time of each kernel variant in units of one 128 x 256 tile on one
+// SM: waves x relative tile cost.  The single-CTA kernels are fill-bound (more
+// so the narrower the tile; factors from measured 8192^3 and 4096 x 768 x 4096
+// runs); a pair tile takes the time of one 128 x 256 tile.  The number of
+// resident pairs differs between parts (GPCs with an odd SM count strand one).
+int choose_block_n(int M, int N, int K, int sms, int pairs) {
+  const int tiles_m = (M + kBlockM - 1) / kBlockM;
+  auto waves = [](long long tiles, int slots) { return (double)((tiles + slots - 1) / slots); };
+  auto single = [&](int bn, double eff) {
+    return waves((long long)tiles_m * ((N + bn - 1) / bn), sms) * (bn / 256.0) * eff;
+  };
+  double best = single(128, 1.45);
+  int pick = 128;
+  if (N > 128 && single(192, 1.20) < best) best = single(192, 1.20), pick = 192;
+  if (N > 192 && single(256, 1.12) < best) best = single(256, 1.12), pick = 256;
+  if (pair_kernel_enabled() && N > 128 && pairs > 0) {
+    GemmShape s{M, N, K, tiles_m, (N + 255) / 256, 0, 0, 1, 16};
+    const int num_kb = (K + kBlockK - 1) / kBlockK;
+    plan_split_tail(s, pairs, num_kb, split_tail_enabled() ? kMaxSplit : 1);
+    const int ptiles = pair_tile_count(s);
+    double cost;
+    if (s.split_s > 1) cost = s.split_first / pairs + 1.0 / s.split_s + 0.1;
+    else cost = waves(ptiles, pairs);
+    if (K < 1024) cost *= 1.25;  // short K: the epilogue of a 256-row tile is not hidden (measured at K = 512)
+    if (cost < best) best = cost, pick = 512;
+  }
+  return pick;
 }
 
 cudaError_t launch_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, int lda,
@@ -184,12 +281,20 @@ cudaError_t launch_gemm_bf16(const void* a, const void* b, void* c, int M, int N
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (block_n == 0) {
-    const long long t256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
-    // CTA pairs once every pair has a tile and K is long enough to hide the epilogue
-    if (pair_kernel_enabled() && N >= 256 && t256 / 2 >= sms / 2 && K >= 1024) block_n = 512;
-    else block_n = (N >= 256 && t256 >= sms / 2) ? 256 : 128;
+    static int pairs = -1;
+    if (pairs < 0) {
+      pairs = 0;
+      if (cudaFuncSetAttribute(gemm_persistent_pair<StoreLocal>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               PairGemmKernel::kSmemBytes) == cudaSuccess)
+        pairs = max_resident_pairs(reinterpret_cast<const void*>(gemm_persistent_pair<StoreLocal>),
+                                   PairGemmKernel::kSmemBytes, sms);
+      else
+        (void)cudaGetLastError();
+    }
+    block_n = choose_block_n(M, N, K, sms, pairs);
   }
   if (block_n == 512) return launch_gemm_pair(a, b, c, M, N, K, lda, ldb, ldc, sms, error_word, stream);
+  if (block_n == 192) return launch_gemm_bn<192>(a, b, c, M, N, K, lda, ldb, ldc, sms, error_word, stream);
   if (block_n == 256) return launch_gemm_bn<256>(a, b, c, M, N, K, lda, ldb, ldc, sms, error_word, stream);
   if (block_n == 128) return launch_gemm_bn<128>(a, b, c, M, N, K, lda, ldb, ldc, sms, error_word, stream);
   return cudaErrorInvalidValue;

@@ -14,7 +14,7 @@ cudaError_t make_tile_map(CUtensorMap* map, const void* base, uint64_t rows, uin
                           uint64_t row_stride_elems, uint32_t box_rows);
 
 // C[M, N] = A[M, K] * B[N, K]^T, bf16, row-major with leading dimensions lda /
-// ldb / ldc (elements).  K, lda, ldb multiples of 8.  block_n: 0 (choose), 128 or
+// ldb / ldc (elements).  K, lda, ldb multiples of 8.  block_n: 0 (choose), 128, 192 or
 // 256 (one CTA per 128 x block_n tile), or 512 = 256 x 256 tiles computed by CTA
 // pairs (cta_group::2).  error_word: device word that receives a GemmError code if a pipeline
 // wait runs out (stays 0 otherwise).
@@ -27,6 +27,13 @@ cudaError_t launch_gemm_bf16(const void* a, const void* b, void* c, int M, int N
 int max_resident_pairs(const void* kernel, int smem_bytes, int sms);
 // False when PENNY_GEMM_PAIR=0 forces the single-CTA kernels everywhere.
 bool pair_kernel_enabled();
+// Whether the ragged last wave of the pair kernel is split along K over the idle
+// pairs.  Off unless PENNY_GEMM_SPLIT_TAIL=1 or set_split_tail(1); set_split_tail(-1)
+// goes back to the environment's choice.
+bool split_tail_enabled();
+void set_split_tail(int on);
+// The block_n that launch_gemm_bf16(block_n = 0) would use (128, 192, 256 or 512 = CTA pairs).
+int choose_block_n(int M, int N, int K, int sms, int pairs);
 
 }  // namespace sm100
 }  // namespace penny

@@ -22,6 +22,14 @@ struct GemmShape {
   // blocks, M fastest inside a band, so that the tiles in flight at one time
   // cover a square-ish patch of C and A's band stays in L2 from wave to wave
   int group_m;
+  // CTA-pair kernel only.  split_s > 1: the pair tiles from split_first on (the
+  // ragged last wave) are each cut into split_s ranges of K steps that different
+  // pairs compute at the same time; partial sums go through split_ws (fp32) and
+  // the last pair to finish a tile adds them up and runs the epilogue.
+  int split_first = 0;
+  int split_s = 0;
+  float* split_ws = nullptr;           // [items][2 CTAs][64 column vectors][128 rows] float4
+  unsigned* split_counters = nullptr;  // [tail tiles][2 CTAs], zero between launches
 };
 
 // Tile index -> (row index before rotation, column block) for `rows_m` rows
@@ -61,6 +69,47 @@ PENNY_TILE_HD void decode_pair_tile(const GemmShape& s, int tile, int r, int& m_
   const int rows = pair_rows(s);
   tile_order(s, tile, rows, s.group_m >> 1, pm_raw, n_blk);
   m_blk = 2 * ((pm_raw + (s.m_rot >> 1)) % rows) + r;
+}
+
+// One unit of work of a CTA pair: K steps [kb0, kb1) of pair tile `tile`;
+// seg is the index of the range within a split tile (0 when not split).
+struct PairWork {
+  int tile, kb0, kb1, seg;
+};
+
+// Decides the split of the last, ragged wave for a grid of `npairs` pairs (all
+// of them resident).  Leaves split_s = 1 when there is nothing to gain.
+PENNY_TILE_HD void plan_split_tail(GemmShape& s, int npairs, int num_kb, int max_split) {
+  const int total = pair_tile_count(s);
+  const int full = (total / npairs) * npairs, rest = total - full;
+  s.split_first = total;
+  s.split_s = 1;
+  if (rest == 0) return;
+  int S = npairs / rest;
+  if (S > max_split) S = max_split;
+  while (S > 1 && num_kb < 4 * S) --S;  // at least four K steps per range
+  if (S < 2) return;
+  s.split_first = full;
+  s.split_s = S;
+}
+
+// The it-th unit of pair `pair` (of npairs); false when it has no more.
+PENNY_TILE_HD bool pair_work(const GemmShape& s, int num_kb, int pair, int npairs, int it, PairWork& w) {
+  const int total = pair_tile_count(s);
+  const int first = (s.split_s > 1) ? s.split_first : total;
+  const int t = pair + it * npairs;
+  if (t < first) {
+    w.tile = t; w.kb0 = 0; w.kb1 = num_kb; w.seg = 0;
+    return true;
+  }
+  if (s.split_s <= 1) return false;
+  const int j = t - first;
+  if (j >= npairs || j >= (total - first) * s.split_s) return false;
+  w.tile = first + j / s.split_s;
+  w.seg = j % s.split_s;
+  w.kb0 = (int)((long long)w.seg * num_kb / s.split_s);
+  w.kb1 = (int)((long long)(w.seg + 1) * num_kb / s.split_s);
+  return true;
 }
 
 }  // namespace sm100

@@ -333,4 +333,17 @@ int penny_gemm_tile_at(int tiles_m, int tiles_n, int m_rot, int m_fastest, int g
   penny::sm100::decode_pair_tile(s, tile, pair_rank, *m_blk, *n_blk);
   return penny::sm100::pair_tile_count(s);
 }
+// The it-th work unit of CTA pair `pair` of `npairs` after planning the split of
+// the last wave: out = {tile, kb0, kb1, seg, split_s, split_first}; 0 when the pair
+// has no such unit.
+int penny_gemm_pair_work(int tiles_m, int tiles_n, int npairs, int num_kb, int max_split, int pair,
+                         int it, int* out) {
+  penny::sm100::GemmShape s{0, 0, 0, tiles_m, tiles_n, 0, tiles_m * tiles_n, 1, 16};
+  penny::sm100::plan_split_tail(s, npairs, num_kb, max_split);
+  penny::sm100::PairWork w{0, 0, 0, 0};
+  const bool ok = penny::sm100::pair_work(s, num_kb, pair, npairs, it, w);
+  out[0] = w.tile; out[1] = w.kb0; out[2] = w.kb1; out[3] = w.seg;
+  out[4] = s.split_s; out[5] = s.split_first;
+  return ok ? 1 : 0;
+}
 }

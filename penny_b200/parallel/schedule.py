@@ -100,3 +100,14 @@ def gemm_tile_at(tiles_m: int, tiles_n: int, tile: int, m_rot: int = 0, m_fastes
     total = lib.penny_gemm_tile_at(tiles_m, tiles_n, m_rot, m_fastest, group_m, pair_rank, tile,
                                    ctypes.byref(m), ctypes.byref(n))
     return m.value, n.value, total
+
+
+def gemm_pair_work(tiles_m: int, tiles_n: int, npairs: int, num_kb: int, pair: int, it: int, max_split: int = 8):
+    """The it-th work unit of CTA pair `pair`: dict(tile, kb0, kb1, seg, split_s, split_first) or None.
+    The ragged last wave of pair tiles is split along K over the idle pairs (csrc/gemm_tile_order.h)."""
+    lib = sim_lib()
+    out = (ctypes.c_int * 6)()
+    ok = lib.penny_gemm_pair_work(tiles_m, tiles_n, npairs, num_kb, max_split, pair, it, out)
+    if not ok:
+        return None
+    return dict(zip(("tile", "kb0", "kb1", "seg", "split_s", "split_first"), list(out)))

@@ -123,3 +123,48 @@ def test_gemm_tile_order_band_is_squareish():
     assert len({m for m, _ in wave}) == 16 and len({n for _, n in wave}) == 10
     flat = [schedule.gemm_tile_at(64, 32, t, group_m=0)[:2] for t in range(148)]
     assert len({m for m, _ in flat}) == 64 and len({n for _, n in flat}) == 3
+
+
+@pytest.mark.parametrize("tiles_m,tiles_n,num_kb", [(32, 14, 64), (32, 16, 64), (64, 32, 128), (1, 16, 64), (1, 7, 64),
+                                                   (13, 11, 24), (3, 3, 5), (32, 3, 64), (2, 2, 4), (32, 16, 8)])
+def test_gemm_split_tail_covers_every_k_step_once(tiles_m, tiles_n, num_kb):
+    """Full waves plus the K-split last wave: every (pair tile, K step) is computed by
+    exactly one CTA pair, a pair gets at most one split unit and it comes last, and
+    the ranges of a split tile are numbered 0..split_s-1."""
+    from penny_b200.parallel import schedule
+    npairs = 74
+    ptiles = ((tiles_m + 1) // 2) * tiles_n
+    seen = {}
+    segs = {}
+    for pair in range(npairs):
+        it, had_split = 0, False
+        while True:
+            w = schedule.gemm_pair_work(tiles_m, tiles_n, npairs, num_kb, pair, it)
+            if w is None:
+                break
+            assert not had_split, "a split unit must be the last unit of its pair"
+            if w["split_s"] > 1 and w["tile"] >= w["split_first"]:
+                had_split = True
+                assert w["kb1"] - w["kb0"] >= 4
+                segs.setdefault(w["tile"], []).append(w["seg"])
+            else:
+                assert (w["kb0"], w["kb1"], w["seg"]) == (0, num_kb, 0)
+            for kb in range(w["kb0"], w["kb1"]):
+                assert (w["tile"], kb) not in seen
+                seen[(w["tile"], kb)] = pair
+            it += 1
+            assert it < 10000
+    assert len(seen) == ptiles * num_kb
+    for tile, ss in segs.items():
+        assert sorted(ss) == list(range(len(ss))) and len(ss) >= 2
+
+
+def test_gemm_split_tail_plan_examples():
+    from penny_b200.parallel import schedule
+    # 224 pair tiles on 74 pairs: three full waves, the two leftover tiles cut 8 ways
+    w = schedule.gemm_pair_work(32, 14, 74, 64, 0, 3)
+    assert (w["split_first"], w["split_s"], w["tile"], w["kb0"], w["kb1"]) == (222, 8, 222, 0, 8)
+    # an exact multiple of the grid is never split
+    assert schedule.gemm_pair_work(4, 37, 74, 64, 0, 0)["split_s"] == 1
+    # too few K steps for even two ranges of four
+    assert schedule.gemm_pair_work(3, 3, 74, 5, 0, 0)["split_s"] == 1

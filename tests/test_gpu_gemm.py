@@ -9,9 +9,11 @@ def ref(a, b):
     return a.float() @ b.float().t()
 
 
-@pytest.mark.parametrize("block_n", [128, 256, 512])  # 512: 256 x 256 tiles on CTA pairs (cta_group::2)
+# 512: 256 x 256 tiles on CTA pairs (cta_group::2), the ragged last wave split along K; 0: chosen by the cost model
+@pytest.mark.parametrize("block_n", [128, 192, 256, 512, 0])
 @pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (300, 520, 264), (1, 4096, 4096),
-                                   (64, 1792, 4096), (4096, 768, 4096), (1000, 3584, 1024)])
+                                   (64, 1792, 4096), (4096, 768, 4096), (1000, 3584, 1024),
+                                   (1600, 2800, 1536)])  # 77 pair tiles on 74 pairs: 3 leftover tiles, 6 K ranges each
 def test_gemm_matches_fp32(shape, block_n):
     from penny_b200._ext import ops
     M, N, K = shape
@@ -38,6 +40,31 @@ def test_gemm_strided_operands_and_repeat():
     assert ops.gemm_error() == 0
     torch.testing.assert_close(c.float(), ref(a, b), atol=0.2, rtol=1.6e-2)
     assert torch.all(big_c[:, N:] == 0)
+
+
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (64, 1792, 4096), (1600, 2800, 1536), (4096, 3584, 1024)])
+def test_gemm_split_tail_repeats(shape):
+    """The ragged last wave of the CTA-pair kernel split along K (opt-in): partial
+    sums go through a workspace, the last pair to arrive adds them up.  The arrival
+    counters live in device memory and reset themselves, so back-to-back launches
+    with different operands must each be right."""
+    from penny_b200._ext import ops
+    M, N, K = shape
+    ops.gemm_set_split_tail(1)
+    try:
+        outs, wants = [], []
+        for i in range(3):
+            a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+            b = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+            out = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+            ops.gemm_bf16(a, b, out, 512)
+            outs.append(out)
+            wants.append(ref(a, b))
+        assert ops.gemm_error() == 0
+        for out, want in zip(outs, wants):
+            torch.testing.assert_close(out.float(), want, atol=2e-2 * (K ** 0.5) * 0.25 + 1e-2, rtol=1.6e-2)
+    finally:
+        ops.gemm_set_split_tail(-1)
 
 
 def test_fused_gemm_kernels_single_rank():
@@ -89,5 +116,9 @@ def test_fused_gemm_kernels_single_rank_cta_pairs():
             assert ops.gemm_error() == 0
             comm.check()
             torch.testing.assert_close(out2.float(), want, atol=0.3, rtol=1.6e-2)
+            out3 = comm.all_gather_gemm(a, w[:768].contiguous())  # 128 x 192 tiles: 128 of them instead of 96
+            assert ops.gemm_error() == 0
+            comm.check()
+            torch.testing.assert_close(out3.float(), want[:, :768], atol=0.3, rtol=1.6e-2)
     finally:
         comm.close()
