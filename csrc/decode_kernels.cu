@@ -8,6 +8,7 @@
 // bytes in flight per SM.  The reference ships no model code at all; these
 // kernels exist so that the TP-decode benchmark runs on this library's own
 // kernels end to end (the GEMMs go to cuBLAS).
+#include "kernel_setup.h"
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -444,13 +445,8 @@ cudaError_t launch_decode_attention(const void* qkv, const void* kcache, const v
   cudaError_t rc = cudaSuccess;
 #define PENNY_ATTN(GG)                                                                            \
   do {                                                                                            \
-    static bool attr_set = false;                                                                 \
-    if (!attr_set) {                                                                              \
-      rc = cudaFuncSetAttribute(k_decode_attn<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
-                                kAttnSmem);                                                       \
-      if (rc != cudaSuccess) return rc;                                                           \
-      attr_set = true;                                                                            \
-    }                                                                                             \
+    rc = kernel_setup(reinterpret_cast<const void*>(k_decode_attn<GG>), kAttnSmem).rc;            \
+    if (rc != cudaSuccess) return rc;                                                             \
     k_decode_attn<GG><<<grid, kAttnWarps * 32, kAttnSmem, stream>>>(                              \
         (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache,    \
         positions, (__nv_bfloat16*)out, part_o, part_ml, Hq, Hkv, max_len, splits, scale);        \

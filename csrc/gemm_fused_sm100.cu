@@ -34,6 +34,7 @@
 #include "gemm_kernel_pair_sm100.cuh"
 #include "gemm_kernel_sm100.cuh"
 #include "gemm_sm100.h"
+#include "kernel_setup.h"
 
 namespace penny {
 namespace sm100 {
@@ -206,11 +207,6 @@ struct AgGemmPolicy : PolicyBase {
   }
 };
 
-template <class K>
-cudaError_t set_smem(K kernel, int bytes) {
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-}
-
 int sm_count() {
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
@@ -238,25 +234,18 @@ cudaError_t launch_gemm_rs(const CommCtx& c, size_t scratch_off, size_t scratch_
     return cudaErrorInvalidValue;
   using Policy = GemmRsPolicy<BN>;
   const int sms = sm_count();
-  static int pairs = 0;
-  if (pairs == 0) {
-    cudaError_t rc0 = set_smem(gemm_persistent_pair<Policy>, PairGemmKernel::kSmemBytes);
-    if (rc0 != cudaSuccess) return rc0;
-    pairs = max_resident_pairs(reinterpret_cast<const void*>(gemm_persistent_pair<Policy>),
-                               PairGemmKernel::kSmemBytes, sms);
-  }
+  const KernelSetup ks = kernel_setup(reinterpret_cast<const void*>(gemm_persistent_pair<Policy>),
+                                      PairGemmKernel::kSmemBytes, kGemmThreads);
+  if (ks.rc != cudaSuccess) return ks.rc;
+  const int pairs = ks.pairs;
   const bool pair = pair_kernel_enabled() && tps % 2 == 0 && (tiles_m / 2) * tiles_n >= pairs && K >= 1024;
   CUtensorMap ma, mb;
   cudaError_t rc = make_tile_map(&ma, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, kBlockM);
   if (rc != cudaSuccess) return rc;
   rc = make_tile_map(&mb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, pair ? BN / 2 : BN);
   if (rc != cudaSuccess) return rc;
-  static bool attr = false;
-  if (!attr) {
-    rc = set_smem(gemm_persistent<BN, Policy>, GemmKernel<BN>::kSmemBytes);
-    if (rc != cudaSuccess) return rc;
-    attr = true;
-  }
+  rc = kernel_setup(reinterpret_cast<const void*>(gemm_persistent<BN, Policy>), GemmKernel<BN>::kSmemBytes).rc;
+  if (rc != cudaSuccess) return rc;
   const int grid = pair ? 2 * std::min(pairs, (tiles_m / 2) * tiles_n) : std::min(sms, tiles_m * tiles_n);
   Policy pol;
   pol.c = c;
@@ -299,13 +288,10 @@ cudaError_t launch_ag_gemm(const CommCtx& c, size_t scratch_off, size_t scratch_
   }
   const int tiles_n = (N + BN - 1) / BN;
   (void)side_ctas;  // kept for API compatibility: the pushes are done by copy warps of every CTA
-  static int pairs = 0;
-  if (pairs == 0) {
-    cudaError_t rc0 = set_smem(gemm_persistent_pair<AgGemmPolicy>, PairGemmKernel::kSmemBytes);
-    if (rc0 != cudaSuccess) return rc0;
-    pairs = max_resident_pairs(reinterpret_cast<const void*>(gemm_persistent_pair<AgGemmPolicy>),
-                               PairGemmKernel::kSmemBytes, sms);
-  }
+  const KernelSetup ks = kernel_setup(reinterpret_cast<const void*>(gemm_persistent_pair<AgGemmPolicy>),
+                                      PairGemmKernel::kSmemBytes, kGemmThreads);
+  if (ks.rc != cudaSuccess) return ks.rc;
+  const int pairs = ks.pairs;
   const bool pair = pair_kernel_enabled() && BN == 256 && tps % 2 == 0 && (tiles_m / 2) * tiles_n >= pairs &&
                     K >= 1024;
   const int grid = pair ? 2 * std::min(pairs, (tiles_m / 2) * tiles_n)
@@ -338,30 +324,18 @@ cudaError_t launch_ag_gemm(const CommCtx& c, size_t scratch_off, size_t scratch_
     gemm_persistent_pair<AgGemmPolicy><<<grid, kGemmThreads, PairGemmKernel::kSmemBytes, stream>>>(
         ma, mb, shape, pol, error_word);
   } else if (BN == 192) {
-    static bool attr = false;
-    if (!attr) {
-      rc = set_smem(gemm_persistent<192, AgGemmPolicy>, GemmKernel<192>::kSmemBytes);
-      if (rc != cudaSuccess) return rc;
-      attr = true;
-    }
+    rc = kernel_setup(reinterpret_cast<const void*>(gemm_persistent<192, AgGemmPolicy>), GemmKernel<192>::kSmemBytes).rc;
+    if (rc != cudaSuccess) return rc;
     gemm_persistent<192, AgGemmPolicy><<<grid, kGemmThreads, GemmKernel<192>::kSmemBytes, stream>>>(
         ma, mb, shape, pol, error_word);
   } else if (BN == 256) {
-    static bool attr = false;
-    if (!attr) {
-      rc = set_smem(gemm_persistent<256, AgGemmPolicy>, GemmKernel<256>::kSmemBytes);
-      if (rc != cudaSuccess) return rc;
-      attr = true;
-    }
+    rc = kernel_setup(reinterpret_cast<const void*>(gemm_persistent<256, AgGemmPolicy>), GemmKernel<256>::kSmemBytes).rc;
+    if (rc != cudaSuccess) return rc;
     gemm_persistent<256, AgGemmPolicy><<<grid, kGemmThreads, GemmKernel<256>::kSmemBytes, stream>>>(
         ma, mb, shape, pol, error_word);
   } else {
-    static bool attr = false;
-    if (!attr) {
-      rc = set_smem(gemm_persistent<128, AgGemmPolicy>, GemmKernel<128>::kSmemBytes);
-      if (rc != cudaSuccess) return rc;
-      attr = true;
-    }
+    rc = kernel_setup(reinterpret_cast<const void*>(gemm_persistent<128, AgGemmPolicy>), GemmKernel<128>::kSmemBytes).rc;
+    if (rc != cudaSuccess) return rc;
     gemm_persistent<128, AgGemmPolicy><<<grid, kGemmThreads, GemmKernel<128>::kSmemBytes, stream>>>(
         ma, mb, shape, pol, error_word);
   }

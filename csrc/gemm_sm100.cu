@@ -35,6 +35,7 @@
 #include <string>
 
 #include "gemm_kernel_pair_sm100.cuh"
+#include "kernel_setup.h"
 #include "gemm_kernel_sm100.cuh"
 
 namespace penny {
@@ -101,13 +102,8 @@ cudaError_t launch_gemm_bn(const void* a, const void* b, void* c, int M, int N, 
   rc = make_tile_map(&mb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN);
   if (rc != cudaSuccess) return rc;
   using Kernel = GemmKernel<BN>;
-  static bool attr = false;
-  if (!attr) {
-    rc = cudaFuncSetAttribute(gemm_persistent<BN, StoreLocal>,
-                              cudaFuncAttributeMaxDynamicSharedMemorySize, Kernel::kSmemBytes);
-    if (rc != cudaSuccess) return rc;
-    attr = true;
-  }
+  rc = kernel_setup(reinterpret_cast<const void*>(gemm_persistent<BN, StoreLocal>), Kernel::kSmemBytes).rc;
+  if (rc != cudaSuccess) return rc;
   const int tiles_m = (M + kBlockM - 1) / kBlockM, tiles_n = (N + BN - 1) / BN;
   const int grid = std::min(sms, tiles_m * tiles_n);
   GemmShape shape{M, N, K, tiles_m, tiles_n, 0, tiles_m * tiles_n, 1, 16};
@@ -117,27 +113,6 @@ cudaError_t launch_gemm_bn(const void* a, const void* b, void* c, int M, int N, 
   gemm_persistent<BN, StoreLocal><<<grid, kGemmThreads, Kernel::kSmemBytes, stream>>>(
       ma, mb, shape, ep, error_word);
   return cudaGetLastError();
-}
-
-// How many CTA pairs of `kernel` the device can hold at once (the persistent grid).
-int max_resident_pairs(const void* kernel, int smem_bytes, int sms) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)sms & ~1u, 1, 1);
-  cfg.blockDim = dim3(kGemmThreads, 1, 1);
-  cfg.dynamicSmemBytes = (size_t)smem_bytes;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
-    (void)cudaGetLastError();
-    n = sms / 2 - 2;  // conservative: a GPC with an odd SM count strands one SM
-  }
-  return std::min(n, sms / 2);
 }
 
 namespace {
@@ -208,14 +183,10 @@ cudaError_t launch_gemm_pair(const void* a, const void* b, void* c, int M, int N
   if (rc != cudaSuccess) return rc;
   rc = make_tile_map(&mb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, PairGemmKernel::kTileN / 2);
   if (rc != cudaSuccess) return rc;
-  static int pairs = 0;
-  if (pairs == 0) {
-    rc = cudaFuncSetAttribute(gemm_persistent_pair<StoreLocal>,
-                              cudaFuncAttributeMaxDynamicSharedMemorySize, PairGemmKernel::kSmemBytes);
-    if (rc != cudaSuccess) return rc;
-    pairs = max_resident_pairs(reinterpret_cast<const void*>(gemm_persistent_pair<StoreLocal>),
-                               PairGemmKernel::kSmemBytes, sms);
-  }
+  const KernelSetup ks = kernel_setup(reinterpret_cast<const void*>(gemm_persistent_pair<StoreLocal>),
+                                      PairGemmKernel::kSmemBytes, kGemmThreads);
+  if (ks.rc != cudaSuccess) return ks.rc;
+  const int pairs = ks.pairs;
   const int tiles_m = (M + kBlockM - 1) / kBlockM;
   const int tiles_n = (N + PairGemmKernel::kTileN - 1) / PairGemmKernel::kTileN;
   const int ptiles = ((tiles_m + 1) / 2) * tiles_n;
@@ -281,16 +252,9 @@ cudaError_t launch_gemm_bf16(const void* a, const void* b, void* c, int M, int N
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (block_n == 0) {
-    static int pairs = -1;
-    if (pairs < 0) {
-      pairs = 0;
-      if (cudaFuncSetAttribute(gemm_persistent_pair<StoreLocal>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               PairGemmKernel::kSmemBytes) == cudaSuccess)
-        pairs = max_resident_pairs(reinterpret_cast<const void*>(gemm_persistent_pair<StoreLocal>),
-                                   PairGemmKernel::kSmemBytes, sms);
-      else
-        (void)cudaGetLastError();
-    }
+    const KernelSetup ks = kernel_setup(reinterpret_cast<const void*>(gemm_persistent_pair<StoreLocal>),
+                                        PairGemmKernel::kSmemBytes, kGemmThreads);
+    const int pairs = ks.rc == cudaSuccess ? ks.pairs : 0;
     block_n = choose_block_n(M, N, K, sms, pairs);
   }
   if (block_n == 512) return launch_gemm_pair(a, b, c, M, N, K, lda, ldb, ldc, sms, error_word, stream);

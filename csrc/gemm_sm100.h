@@ -22,9 +22,6 @@ cudaError_t launch_gemm_bf16(const void* a, const void* b, void* c, int M, int N
                              int ldb, int ldc, int block_n, uint32_t* error_word,
                              cudaStream_t stream);
 
-// Number of CTA pairs (clusters of two) of `kernel` that can be resident at once
-// with `smem_bytes` of dynamic shared memory: the grid of the pair kernels.
-int max_resident_pairs(const void* kernel, int smem_bytes, int sms);
 // False when PENNY_GEMM_PAIR=0 forces the single-CTA kernels everywhere.
 bool pair_kernel_enabled();
 // Whether the ragged last wave of the pair kernel is split along K over the idle
