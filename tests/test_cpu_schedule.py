@@ -168,3 +168,17 @@ def test_gemm_split_tail_plan_examples():
     assert schedule.gemm_pair_work(4, 37, 74, 64, 0, 0)["split_s"] == 1
     # too few K steps for even two ranges of four
     assert schedule.gemm_pair_work(3, 3, 74, 5, 0, 0)["split_s"] == 1
+
+
+def test_cpp_schedule_properties(tmp_path):
+    """The same headers the kernels include, compiled as plain C++ and checked
+    exhaustively (rings are Hamiltonian, send/receive chunks pair up, every chunk
+    is reduced exactly once, GEMM tile and K-step lists are exact covers)."""
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = tmp_path / "schedule_test"
+    subprocess.check_call(["g++", "-O1", "-std=c++17", "-o", str(exe), os.path.join(root, "tests", "cpp", "schedule_test.cpp")])
+    out = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "schedule_test ok" in out.stdout
