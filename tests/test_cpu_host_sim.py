@@ -63,3 +63,25 @@ def test_missing_rank_times_out_cleanly(algo):
     waited_for = {status[r][2] for r in range(world) if r != 1 and status[r][0] != 0}
     # somebody was directly waiting for the missing rank
     assert 1 in waited_for or algo in ("ring_standard", "double_ring", "tree")
+
+
+def test_protocols_under_thread_sanitizer(tmp_path):
+    """Every protocol once more with the simulator compiled with -fsanitize=thread:
+    ranks and blocks are real threads there, so a missing release / acquire between a
+    flag and the data it guards, or a scratch slot reused one call too early, shows
+    up as a reported race."""
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    probe = tmp_path / "probe.cpp"
+    probe.write_text("int main() { return 0; }\n")
+    if subprocess.run(["g++", "-fsanitize=thread", "-o", str(tmp_path / "probe"), str(probe)],
+                      capture_output=True).returncode != 0:
+        pytest.skip("g++ has no ThreadSanitizer runtime here")
+    exe = tmp_path / "sim_tsan"
+    subprocess.check_call(["g++", "-O1", "-g", "-std=c++17", "-fsanitize=thread", "-pthread", "-w", "-o", str(exe),
+                           os.path.join(root, "tests", "cpp", "sim_tsan_main.cpp")])
+    out = subprocess.run([str(exe)], capture_output=True, text=True, timeout=600,
+                         env=dict(os.environ, TSAN_OPTIONS="halt_on_error=0 report_signal_unsafe=0"))
+    assert "ThreadSanitizer" not in out.stderr, out.stderr[-3000:]
+    assert out.returncode == 0 and "sim_tsan ok" in out.stdout, out.stdout[-500:] + out.stderr[-1500:]
