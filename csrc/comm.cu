@@ -577,4 +577,20 @@ void Communicator::host_barrier() {
   if (bs_) bs_->barrier();
 }
 
+void Communicator::poison_scratch() {
+  cudaDeviceSynchronize();
+  host_barrier();  // nobody is still reading or writing a peer's scratch
+  const Region* regions[] = {&scratch_, &scratch_ll_, &scratch_pair_, &stage_in_, &stage_out_, &ag_region_};
+  for (const Region* r : regions) {
+    if (r->bytes == 0) continue;
+    for (int v = 0; v < views(); ++v) {
+      cudaError_t rc = cudaMemset(local_ptr(r->off, v), 0xFF, r->bytes);
+      if (rc != cudaSuccess)
+        throw std::runtime_error(std::string("penny: poison_scratch: ") + cudaGetErrorString(rc));
+    }
+  }
+  cudaDeviceSynchronize();
+  host_barrier();  // nobody starts the next call before every heap is poisoned
+}
+
 }  // namespace penny

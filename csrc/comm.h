@@ -110,6 +110,12 @@ class Communicator {
   // Reads (and optionally clears) the status words; synchronises the device.
   StatusRecord read_status(int view, bool clear);
   void host_barrier();
+  // Debug aid: with every rank idle (device synchronised, host barrier on both
+  // sides) overwrites every scratch region this communicator has allocated with
+  // 0xFF bytes (NaN in every float format, never a valid flag or stamp), so a
+  // kernel that reads scratch it was not sent in the current call returns NaNs
+  // instead of the previous call's plausible numbers.  Collective: all ranks call it.
+  void poison_scratch();
   void set_timeout_ms(int ms);
   void destroy();
 

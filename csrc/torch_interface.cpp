@@ -219,6 +219,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("comm_views", [](int64_t h) { return as_comm(h)->views(); });
   m.def("comm_heap_free", [](int64_t h) { return (int64_t)as_comm(h)->heap_free_bytes(); });
   m.def("comm_barrier", [](int64_t h) { as_comm(h)->host_barrier(); });
+  m.def("comm_poison_scratch", [](int64_t h) { as_comm(h)->poison_scratch(); });
   m.def("comm_set_timeout_ms", [](int64_t h, int ms) { as_comm(h)->set_timeout_ms(ms); });
   m.def("comm_pick_algo", [](int64_t h, int dtype, int64_t n) { return as_comm(h)->pick_algo(dtype, (size_t)n); });
 

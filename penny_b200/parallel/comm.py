@@ -22,6 +22,7 @@ from typing import List, Optional, Sequence, Union
 import torch
 
 from .._ext import ops
+from ..config import PennyConfig
 
 TensorOrList = Union[torch.Tensor, Sequence[torch.Tensor]]
 
@@ -77,27 +78,47 @@ class Communicator:
         self.views = ops.comm_views(handle)
         # data_ptr of tensors handed out by empty(): symmetric by construction
         self._symmetric = {}
+        # PennyConfig.debug_poison: check() also overwrites all scratch with NaN patterns
+        self.debug_poison = False
 
     # ------------------------------------------------------------------ creation
     @classmethod
-    def create(cls, group=None, heap_bytes: Optional[int] = None, multicast: bool = True,
-               heap_mode: str = "auto", timeout_ms: int = 0) -> "Communicator":
+    def create(cls, group=None, heap_bytes: Optional[int] = None, multicast: Optional[bool] = None,
+               heap_mode: Optional[str] = None, timeout_ms: Optional[int] = None,
+               config: Optional[PennyConfig] = None) -> "Communicator":
+        """One communicator over the ranks of `group` (default: the world group).
+
+        Settings come from `config` (default `PennyConfig.from_env()`); the
+        keyword arguments override single fields of it."""
         import torch.distributed as dist
 
+        cfg = config if config is not None else PennyConfig.from_env()
+        if heap_bytes is None:
+            heap_bytes = cfg.heap_bytes
+        if multicast is None:
+            multicast = not cfg.disable_nvls
+        if heap_mode is None:
+            heap_mode = cfg.heap_mode
+        if timeout_ms is None:
+            timeout_ms = cfg.timeout_ms
         rank = dist.get_rank(group)
         world = dist.get_world_size(group)
         box = [bytes(ops.get_unique_id()) if rank == 0 else None]
         src = dist.get_global_rank(group, 0) if group is not None else 0
         dist.broadcast_object_list(box, src=src, group=group, device="cpu")
         mode = {"auto": 0, "vmm": 1, "ipc": 2}[heap_mode]
-        if heap_bytes is None:
-            heap_bytes = int(os.environ.get("PENNY_HEAP_BYTES", 1 << 30))
-        h = ops.comm_create(box[0], rank, world, int(heap_bytes), mode, multicast, int(timeout_ms))
-        return cls(h, emulated=False)
+        h = ops.comm_create(box[0], rank, world, int(heap_bytes), mode, bool(multicast), int(timeout_ms))
+        comm = cls(h, emulated=False)
+        comm.debug_poison = cfg.debug_poison
+        return comm
 
     @classmethod
-    def emulated(cls, world: int, heap_bytes: int = 256 << 20, timeout_ms: int = 2000) -> "Communicator":
-        return cls(ops.comm_create_emulated(world, int(heap_bytes), int(timeout_ms)), emulated=True)
+    def emulated(cls, world: int, heap_bytes: int = 256 << 20, timeout_ms: int = 2000,
+                 debug_poison: Optional[bool] = None) -> "Communicator":
+        """All `world` ranks on ONE GPU (one cooperative launch per collective): for tests and profiling."""
+        comm = cls(ops.comm_create_emulated(world, int(heap_bytes), int(timeout_ms)), emulated=True)
+        comm.debug_poison = PennyConfig.from_env().debug_poison if debug_poison is None else bool(debug_poison)
+        return comm
 
     def close(self):
         if self._h:
@@ -267,11 +288,21 @@ class Communicator:
         return dict(ops.comm_status(self._h, view, clear))
 
     def check(self):
-        """Synchronise and raise PennyTimeoutError if any device-side wait ran out."""
+        """Synchronise and raise PennyTimeoutError if any device-side wait ran out.
+        With `debug_poison` set it then poisons the scratch (see poison_scratch)."""
         recs = [self.status(v, clear=True) for v in range(self.views)]
         for rec in recs:
             if rec["code"] != 0:
                 raise PennyTimeoutError(rec)
+        if self.debug_poison:
+            self.poison_scratch()
+
+    def poison_scratch(self):
+        """Debug aid, collective (every rank calls it): with all ranks idle, fill
+        every scratch region with 0xFF bytes, so that a kernel reading scratch that
+        nobody wrote in the current call produces NaNs rather than the previous
+        call's plausible values."""
+        ops.comm_poison_scratch(self._h)
 
     def wait_selftest(self):
         ops.comm_wait_selftest(self._h)

@@ -17,9 +17,10 @@ _L2_FLUSH = None
 
 
 def initialize_distributed(backend: str = "cpu:gloo,cuda:nccl", heap_bytes: Optional[int] = None,
-                           init_native: bool = True):
+                           init_native: bool = True, config=None):
     """One process per GPU: torch.distributed (gloo for objects, NCCL as the
-    baseline) + the native communicator.  Reads torchrun's environment."""
+    baseline) + the native communicator.  Reads torchrun's environment; `config`
+    (a PennyConfig, default PennyConfig.from_env()) carries the library's knobs."""
     import torch.distributed as dist
 
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -40,25 +41,31 @@ def initialize_distributed(backend: str = "cpu:gloo,cuda:nccl", heap_bytes: Opti
         dist.init_process_group(backend=backend, rank=rank, world_size=world, **kw)
     comm = None
     if init_native and torch.cuda.is_available() and world > 1:
-        comm = global_communicator(heap_bytes=heap_bytes)
+        comm = global_communicator(heap_bytes=heap_bytes, config=config)
     return rank, world, comm
 
 
-def global_communicator(heap_bytes: Optional[int] = None):
-    """The process-wide communicator over the default group (created on first use)."""
+def global_communicator(heap_bytes: Optional[int] = None, config=None):
+    """The process-wide communicator over the default group (created on first use).
+    The native side reads its settings from the environment, so the PennyConfig
+    (env + `heap_bytes` override) is exported there before init_with_uid."""
     global _GLOBAL_COMM
     if _GLOBAL_COMM is None:
         import torch.distributed as dist
         from .._ext import ops
+        from ..config import PennyConfig
         from ..parallel.comm import Communicator
+        cfg = config if config is not None else PennyConfig.from_env(heap_bytes=heap_bytes)
+        if config is not None and heap_bytes is not None:
+            cfg.heap_bytes = int(heap_bytes)
         if not ops.is_initialized():
             # the same two steps as the reference: unique id from rank 0, init on all
             box = [bytes(ops.get_unique_id()) if dist.get_rank() == 0 else None]
             dist.broadcast_object_list(box, src=0, device="cpu")
-            if heap_bytes is not None:
-                os.environ["PENNY_HEAP_BYTES"] = str(int(heap_bytes))
+            cfg.apply_env()
             ops.init_with_uid(box[0], dist.get_rank(), dist.get_world_size())
         _GLOBAL_COMM = Communicator(ops.global_comm(), emulated=False, owned=False)
+        _GLOBAL_COMM.debug_poison = cfg.debug_poison
     return _GLOBAL_COMM
 
 

@@ -1,5 +1,7 @@
 """The Python-visible surface a user of the reference expects, checked without a GPU."""
 import os
+
+import pytest
 import sys
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -62,3 +64,31 @@ except RuntimeError as e:
     # both ranks met in the bootstrap and then failed on the missing GPU, not on the rendezvous
     for o in outs:
         assert o.startswith("error:") and "bootstrap" not in o, outs
+
+
+def test_penny_config_env_and_overrides(monkeypatch):
+    from penny_b200 import PennyConfig
+    for k in ("PENNY_HEAP_BYTES", "PENNY_TIMEOUT_MS", "PENNY_DISABLE_NVLS", "PENNY_HEAP_MODE", "NNODES", "PENNY_ALGO",
+              "VLLM_CUSTOM_ALLREDUCE_ALGO", "PENNY_GEMM_PAIR", "PENNY_GEMM_SPLIT_TAIL", "PENNY_DEBUG_POISON"):
+        monkeypatch.delenv(k, raising=False)
+    d = PennyConfig.from_env()
+    assert (d.heap_bytes, d.timeout_ms, d.disable_nvls, d.heap_mode, d.nnodes) == (1 << 30, 10000, False, "auto", 1)
+    assert d.gemm_pair and not d.gemm_split_tail and not d.debug_poison and d.algo is None
+    monkeypatch.setenv("PENNY_HEAP_BYTES", str(2 << 30))
+    monkeypatch.setenv("PENNY_DISABLE_NVLS", "1")
+    monkeypatch.setenv("PENNY_ALGO", "twoshot")
+    monkeypatch.setenv("NNODES", "2")
+    monkeypatch.setenv("PENNY_GEMM_PAIR", "0")
+    c = PennyConfig.from_env(timeout_ms=250, heap_mode="ipc")
+    assert (c.heap_bytes, c.disable_nvls, c.algo, c.nnodes, c.gemm_pair) == (2 << 30, True, "twoshot", 2, False)
+    assert (c.timeout_ms, c.heap_mode) == (250, "ipc")            # keyword overrides win
+    assert "timeout_ms=250" in c.describe()
+    c.apply_env()
+    import os
+    assert os.environ["PENNY_TIMEOUT_MS"] == "250" and os.environ["PENNY_HEAP_MODE"] == "ipc"
+    with pytest.raises(TypeError):
+        PennyConfig.from_env(no_such_field=1)
+    with pytest.raises(ValueError):
+        PennyConfig.from_env(heap_mode="nvshmem")
+    with pytest.raises(ValueError):
+        PennyConfig.from_env(vllm_algo="3stage")

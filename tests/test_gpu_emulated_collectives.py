@@ -191,3 +191,47 @@ def test_bounded_wait_reports_status(comms):
     outs = comm.all_reduce(ins, algo="oneshot")
     comm.check()
     torch.testing.assert_close(outs[0], ins[0] + ins[1])
+
+
+def test_poisoned_scratch_never_reaches_a_result():
+    """debug_poison: every check() overwrites all scratch regions with 0xFF bytes
+    (NaN in every float format).  A protocol that consumed scratch it was not sent
+    in the current call (a flag satisfied by an older call, a half reused too
+    early) would now produce NaNs instead of plausible old numbers."""
+    from penny_b200.parallel.comm import Communicator
+    world, dtype = 4, torch.bfloat16
+    comm = Communicator.emulated(world, heap_bytes=192 << 20, timeout_ms=3000, debug_poison=True)
+    try:
+        seq = [("twoshot", 300000), ("oneshot_ll", 2048), ("oneshot", 8192), ("ring_standard", 70000),
+               ("ring_simple", 5000), ("tree", 5000), ("double_ring", 33333), ("oneshot_ll", 4096), ("twoshot", 64)] * 2
+        for i, (algo, n) in enumerate(seq):
+            ins = make_inputs(world, n, dtype, seed=100 + i)
+            want = torch.stack([x.float() for x in ins]).sum(0)
+            outs = comm.all_reduce(ins, algo=algo)
+            comm.check()                                   # status, then poison
+            for r in range(world):
+                assert torch.isfinite(outs[r].float()).all(), (algo, n, r)
+                torch.testing.assert_close(outs[r].float(), want, **TOL[dtype])
+        n = 4096 * world
+        ins = make_inputs(world, n, dtype, seed=7)
+        total = torch.stack([x.float() for x in ins]).sum(0)
+        for _ in range(2):
+            rs = comm.reduce_scatter(ins)
+            comm.check()
+            ag = comm.all_gather([x[:1024].contiguous() for x in ins])
+            comm.check()
+            for r in range(world):
+                torch.testing.assert_close(rs[r].float(), total[r * 4096:(r + 1) * 4096], **TOL[dtype])
+                assert torch.equal(ag[r], torch.cat([x[:1024] for x in ins]))
+        w = torch.ones(512, device="cuda", dtype=dtype)
+        for proto in ("ll", "flag"):
+            xs = [torch.randn(8, 512, device="cuda").to(dtype) for _ in range(world)]
+            res = [torch.randn(8, 512, device="cuda").to(dtype) for _ in range(world)]
+            full = torch.stack([x.float() for x in xs]).sum(0) + res[0].float()
+            res_all = [res[0].clone() for _ in range(world)]
+            out, _ = comm.fused_all_reduce_rmsnorm(xs, w, residual=res_all, proto=proto)
+            comm.check()
+            want = full * torch.rsqrt(full.pow(2).mean(-1, keepdim=True) + 1e-5)
+            torch.testing.assert_close(out[0].float(), want, atol=6e-2, rtol=3e-2)
+    finally:
+        comm.close()
