@@ -6,6 +6,7 @@
 #include <pybind11/pybind11.h>
 #include <torch/extension.h>
 
+#include "gemm_skinny_sm100.h"
 #include "gemm_sm100.h"
 
 namespace py = pybind11;
@@ -41,6 +42,25 @@ void bind_gemm(py::module_& m) {
         (int)out.stride(0), (int)block_n, penny_gemm_error_word(), at::cuda::getCurrentCUDAStream().stream());
     TORCH_CHECK(rc == cudaSuccess, "gemm_bf16: ", cudaGetErrorString(rc));
   }, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("block_n") = 0);
+  // Decode-batch linear: out[B, N] = x[B, K] @ w[N, K]^T for B <= 128, streaming w at HBM
+  // speed on all SMs (stream-K).  silu_pairs: w's rows are blocks of 64 gate + 64 up rows and
+  // out is [B, N / 2] = silu(gate) * up.
+  m.def("gemm_skinny", [](at::Tensor x, at::Tensor w, at::Tensor out, bool silu_pairs) {
+    TORCH_CHECK(x.is_cuda() && w.is_cuda() && out.is_cuda(), "gemm_skinny: CUDA tensors");
+    TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 &&
+                    out.scalar_type() == at::kBFloat16, "gemm_skinny: bf16 only");
+    TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm_skinny: 2-D tensors");
+    TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1, "gemm_skinny: rows must be contiguous");
+    const int64_t B = x.size(0), K = x.size(1), N = w.size(0);
+    TORCH_CHECK(B >= 1 && B <= 128, "gemm_skinny: 1 <= rows of x <= 128 (use gemm_bf16 beyond)");
+    TORCH_CHECK(w.size(1) == K && out.size(0) == B && out.size(1) == (silu_pairs ? N / 2 : N),
+                "gemm_skinny: shape mismatch");
+    const at::cuda::OptionalCUDAGuard guard(x.device());
+    cudaError_t rc = penny::sm100::launch_gemm_skinny(
+        x.data_ptr(), w.data_ptr(), out.data_ptr(), (int)B, (int)N, (int)K, (int)x.stride(0), (int)w.stride(0),
+        (int)out.stride(0), silu_pairs ? 1 : 0, penny_gemm_error_word(), at::cuda::getCurrentCUDAStream().stream());
+    TORCH_CHECK(rc == cudaSuccess, "gemm_skinny: ", cudaGetErrorString(rc));
+  }, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("silu_pairs") = false);
   m.def("gemm_set_split_tail", [](int64_t on) { penny::sm100::set_split_tail((int)on); }, py::arg("on"),
         "1 / 0: split (or not) the ragged last wave of the CTA-pair GEMM along K; -1: PENNY_GEMM_SPLIT_TAIL decides");
   // Synchronises; returns and clears the error code of the GEMM kernels (0 = fine).

@@ -33,6 +33,7 @@ CUDA_SOURCES = [
     "csrc/decode_kernels.cu",
     "csrc/gemm_sm100.cu",
     "csrc/gemm_fused_sm100.cu",
+    "csrc/gemm_skinny_sm100.cu",
     "csrc/moe_dispatch_combine.cu",
 ]
 CPP_SOURCES = [
