@@ -13,7 +13,8 @@
 //     partial in a workspace slot and bumps the tile's counter; the CTA that
 //     arrives last adds the partials in CTA order (the result does not depend on
 //     who is last), stores the tile and resets the counter – no spinning, CUDA
-//     graph replays keep working.
+//     graph replays keep working.  The workspace is per device: these GEMMs
+//     must be ordered on the GPU (one stream or one graph), not concurrent.
 //   * warp 0: TMA producer (8-stage ring, 24-32 KB per stage: ~200 KB of weight
 //     bytes in flight per SM); warp 1: MMA issuer, two TMEM accumulators;
 //     warps 2-5: epilogue.  TMEM lane = n, so for each batch row the 32 lanes of
@@ -296,21 +297,25 @@ struct SkinnyScratch {
   size_t ws_bytes = 0, counter_words = 0;
 };
 
-// One workspace per (device, stream); grown on demand, never while the stream is capturing.
+// One workspace per device, grown on demand (never while the stream is being
+// captured: a capture stream is not the stream the warm-up ran on, so the
+// workspace cannot be tied to a stream).  Launches are expected to be ordered on
+// the device – one stream, or one CUDA graph – as the kernels of a decode step
+// are; two of these GEMMs running at the same time on one GPU would share it.
 SkinnyScratch* skinny_scratch(cudaStream_t stream, size_t ws_bytes, size_t counter_words) {
   static std::mutex mu;
-  static std::map<std::pair<int, cudaStream_t>, SkinnyScratch> table;
+  static std::map<int, SkinnyScratch> table;
   int dev = 0;
   cudaGetDevice(&dev);
   std::lock_guard<std::mutex> lock(mu);
-  SkinnyScratch& sc = table[{dev, stream}];
+  SkinnyScratch& sc = table[dev];
   if (sc.ws_bytes >= ws_bytes && sc.counter_words >= counter_words) return &sc;
   cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
   if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
     (void)cudaGetLastError();
     return nullptr;
   }
-  cudaStreamSynchronize(stream);  // nothing in flight still uses the old buffers
+  cudaDeviceSynchronize();  // nothing in flight still uses the old buffers
   if (sc.ws) cudaFree(sc.ws);
   if (sc.counters) cudaFree(sc.counters);
   sc = SkinnyScratch{};

@@ -11,8 +11,10 @@ namespace sm100 {
 // silu_pairs = 1: W's rows come in blocks of 128 = 64 gate rows followed by the
 // 64 up rows of the same features (N a multiple of 128) and
 // out[B, N / 2][b][blk * 64 + i] = silu(gate) * up.
-// The first call on a (device, stream) allocates a workspace and must not be
-// made while that stream is being captured; error_word as in launch_gemm_bf16.
+// The first call on a device (and the first one that needs a larger one) allocates
+// a per-device workspace and must not be made during stream capture; calls must
+// be ordered on the device (one stream or one graph).  error_word as in
+// launch_gemm_bf16.
 cudaError_t launch_gemm_skinny(const void* x, const void* w, void* out, int B, int N, int K, int ldx, int ldw,
                                int ldo, int silu_pairs, uint32_t* error_word, cudaStream_t stream);
 
