@@ -65,23 +65,34 @@ def test_missing_rank_times_out_cleanly(algo):
     assert 1 in waited_for or algo in ("ring_standard", "double_ring", "tree")
 
 
-def test_protocols_under_thread_sanitizer(tmp_path):
-    """Every protocol once more with the simulator compiled with -fsanitize=thread:
-    ranks and blocks are real threads there, so a missing release / acquire between a
-    flag and the data it guards, or a scratch slot reused one call too early, shows
-    up as a reported race."""
+def _sanitizer_run(tmp_path, flags, marker):
     import os
     import subprocess
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     probe = tmp_path / "probe.cpp"
     probe.write_text("int main() { return 0; }\n")
-    if subprocess.run(["g++", "-fsanitize=thread", "-o", str(tmp_path / "probe"), str(probe)],
-                      capture_output=True).returncode != 0:
-        pytest.skip("g++ has no ThreadSanitizer runtime here")
-    exe = tmp_path / "sim_tsan"
-    subprocess.check_call(["g++", "-O1", "-g", "-std=c++17", "-fsanitize=thread", "-pthread", "-w", "-o", str(exe),
+    if subprocess.run(["g++", *flags, "-o", str(tmp_path / "probe"), str(probe)], capture_output=True).returncode != 0:
+        pytest.skip(f"g++ has no runtime for {flags} here")
+    exe = tmp_path / "sim_sanitized"
+    subprocess.check_call(["g++", "-O1", "-g", "-std=c++17", *flags, "-pthread", "-w", "-o", str(exe),
                            os.path.join(root, "tests", "cpp", "sim_tsan_main.cpp")])
-    out = subprocess.run([str(exe)], capture_output=True, text=True, timeout=600,
-                         env=dict(os.environ, TSAN_OPTIONS="halt_on_error=0 report_signal_unsafe=0"))
-    assert "ThreadSanitizer" not in out.stderr, out.stderr[-3000:]
+    env = dict(os.environ, TSAN_OPTIONS="halt_on_error=0 report_signal_unsafe=0", ASAN_OPTIONS="detect_leaks=0")
+    out = subprocess.run([str(exe)], capture_output=True, text=True, timeout=900, env=env)
+    assert marker not in out.stderr and "runtime error" not in out.stderr, out.stderr[-3000:]
     assert out.returncode == 0 and "sim_tsan ok" in out.stdout, out.stdout[-500:] + out.stderr[-1500:]
+
+
+def test_protocols_under_thread_sanitizer(tmp_path):
+    """Every protocol (fp32 and bf16, sizes 1 / 1023 / 1536, 2 and 4 ranks) with the
+    simulator compiled with -fsanitize=thread: ranks and blocks are real threads there,
+    so a missing release / acquire between a flag and the data it guards, or a scratch
+    slot reused one call too early, shows up as a reported race."""
+    _sanitizer_run(tmp_path, ["-fsanitize=thread"], "ThreadSanitizer")
+
+
+def test_protocols_under_address_sanitizer(tmp_path):
+    """The same runs with -fsanitize=address,undefined: the simulated heaps are exactly as
+    large as the scratch the launchers ask for, so an index past a slot, a ragged tail read
+    as a full vector or a misaligned vector access is reported (the bounds checks that
+    compute-sanitizer would do on the device, done on the same code on the CPU)."""
+    _sanitizer_run(tmp_path, ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"], "AddressSanitizer")
