@@ -172,6 +172,36 @@ class CpuCommunicator:
             znew = residual
         return normed, znew
 
+    # ------------------------------------------ sequence-parallel linears (semantics)
+    def gemm_reduce_scatter(self, a: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None):
+        """out[M / world, N] = this rank's row shard of sum_r a_r[M, K_r] @ weight_r[N, K_r]^T
+        (the GPU path fuses the GEMM and the reduce-scatter into one tcgen05 kernel)."""
+        M = a.shape[0]
+        if M % self.world_size:
+            raise ValueError("gemm_reduce_scatter needs M to be a multiple of the world size")
+        partial = (a.float() @ weight.float().t()).to(a.dtype)      # what each rank's GEMM epilogue emits
+        shard = self.reduce_scatter(partial).reshape(M // self.world_size, weight.shape[0])
+        if out is None:
+            return shard
+        out.copy_(shard)
+        return out
+
+    def all_gather_gemm(self, a_shard: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None, **_):
+        """out[M, N] = all_gather(a_shard)[M, K] @ weight[N, K]^T."""
+        full = self.all_gather(a_shard).reshape(a_shard.shape[0] * self.world_size, a_shard.shape[1])
+        res = (full.float() @ weight.float().t()).to(a_shard.dtype)
+        if out is None:
+            return res
+        out.copy_(res)
+        return out
+
+    def empty(self, *shape, dtype=torch.float32):
+        """Counterpart of the symmetric-heap allocation: plain CPU memory here."""
+        return torch.empty(*shape, dtype=dtype)
+
+    def poison_scratch(self):
+        return None
+
     def barrier(self):
         dist.barrier(group=self.group)
 

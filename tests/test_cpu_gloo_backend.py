@@ -65,6 +65,19 @@ def _worker(rank, world, port, out_dir):
             fails.append("fused norm")
         if not torch.allclose(newres, z, atol=1e-6):
             fails.append("fused residual")
+        # sequence-parallel linears: row-parallel GEMM -> reduce-scatter, all-gather -> column-parallel GEMM
+        M, N, K = 8 * world, 24, 16 * world
+        gen = torch.Generator().manual_seed(5)
+        a_full, w_full = torch.randn(M, K, generator=gen), torch.randn(N, K, generator=gen)
+        ks, rows = K // world, M // world
+        want = a_full @ w_full.t()
+        got = comm.gemm_reduce_scatter(a_full[:, rank * ks:(rank + 1) * ks].contiguous(),
+                                       w_full[:, rank * ks:(rank + 1) * ks].contiguous())
+        if got.shape != (rows, N) or not torch.allclose(got, want[rank * rows:(rank + 1) * rows], atol=1e-4):
+            fails.append("gemm_reduce_scatter")
+        got = comm.all_gather_gemm(a_full[rank * rows:(rank + 1) * rows].contiguous(), w_full)
+        if got.shape != (M, N) or not torch.allclose(got, want, atol=1e-4):
+            fails.append("all_gather_gemm")
     finally:
         with open(os.path.join(out_dir, f"r{rank}.txt"), "w") as f:
             f.write("\n".join(fails))
