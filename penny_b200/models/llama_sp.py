@@ -13,7 +13,9 @@ fused INTO the GEMM kernel:
 
 `backend="penny"` uses `Communicator.all_gather_gemm` / `gemm_reduce_scatter`;
 `backend="nccl"` is the baseline: NCCL all_gather_into_tensor / reduce_scatter_tensor
-around cuBLAS GEMMs.  The attention itself is not a communication op and goes
+around cuBLAS GEMMs.  With `device="cpu"` (and a `CpuCommunicator` over gloo) the
+same sharding and layer logic runs on CPU tensors with plain torch ops, which is
+how the model's partitioning is tested without a GPU.  The attention itself is not a communication op and goes
 to the library kernel behind `torch.nn.functional.scaled_dot_product_attention`
 in both backends; norms, RoPE and silu*mul are this library's kernels in both.
 
@@ -56,17 +58,22 @@ class LlamaSPPrefill:
     """`layers` transformer layers over one sequence of `tokens` tokens, sequence-parallel over `world` GPUs."""
 
     def __init__(self, cfg: LlamaConfig, comm=None, rank: int = 0, world: int = 1, tokens: int = 4096,
-                 layers: Optional[int] = None, backend: str = "penny", seed: int = 0, process_group=None):
+                 layers: Optional[int] = None, backend: str = "penny", seed: int = 0, process_group=None,
+                 device: str = "cuda"):
         assert backend in ("penny", "nccl")
         assert cfg.heads % world == 0 and cfg.kv_heads % world == 0 and cfg.ffn % world == 0 and cfg.head_dim == 128
-        assert tokens % (world * 128) == 0, "every rank's sequence shard must be whole 128-row blocks"
+        self.cpu = device == "cpu"
+        if self.cpu:
+            assert tokens % world == 0
+        else:
+            assert tokens % (world * 128) == 0, "every rank's sequence shard must be whole 128-row blocks"
         if backend == "penny":
             assert comm is not None, "the fused kernels need a Communicator (use Communicator.emulated(1) on one GPU)"
         self.cfg, self.comm, self.rank, self.world, self.T = cfg, comm, rank, world, tokens
         self.backend, self.pg = backend, process_group
         self.L = cfg.layers if layers is None else layers
         self.Hq, self.Hkv, self.F = cfg.heads // world, cfg.kv_heads // world, cfg.ffn // world
-        self.dev = torch.device("cuda", torch.cuda.current_device())
+        self.dev = torch.device("cpu") if self.cpu else torch.device("cuda", torch.cuda.current_device())
         D, H, r = cfg.head_dim, cfg.hidden, rank
         self.layers = []
         for w in _full_weights(cfg, self.L, seed, self.dev):
@@ -88,8 +95,8 @@ class LlamaSPPrefill:
         self.part = e(Ts, H)                               # reduce-scattered linear output
         self.gu = e(tokens, 2 * self.F)
         self.act = e(tokens, self.F)
-        self.gathered = e(tokens, H) if backend == "nccl" else None
-        self.full = e(tokens, H) if backend == "nccl" else None
+        self.gathered = e(tokens, H) if backend == "nccl" and not self.cpu else None
+        self.full = e(tokens, H) if backend == "nccl" and not self.cpu else None
         self.scale = 1.0 / math.sqrt(D)
         # kernels of this library per forward: per layer 2 norms, RoPE, silu*mul and (penny) 4 fused GEMMs
         self.kernels_per_forward = self.L * (4 + (4 if backend == "penny" else 0))
@@ -97,7 +104,7 @@ class LlamaSPPrefill:
     # ------------------------------------------------------------------ linears
     def _col(self, h_shard: torch.Tensor, w: torch.Tensor, out: torch.Tensor):
         """Column-parallel linear on the gathered sequence: out[T, n] = all_gather(h_shard) @ w^T."""
-        if self.backend == "penny":
+        if self.backend == "penny" or self.cpu:
             self.comm.all_gather_gemm(h_shard, w, out=out)
         else:
             if self.world > 1:
@@ -108,7 +115,7 @@ class LlamaSPPrefill:
 
     def _row(self, a: torch.Tensor, w: torch.Tensor, out_shard: torch.Tensor):
         """Row-parallel linear, result summed over ranks and scattered along the sequence."""
-        if self.backend == "penny":
+        if self.backend == "penny" or self.cpu:
             self.comm.gemm_reduce_scatter(a, w, out=out_shard)
         else:
             if self.world > 1:
@@ -117,9 +124,40 @@ class LlamaSPPrefill:
             else:
                 torch.matmul(a, w.t(), out=out_shard)
 
+    # ------------------------------------------- elementwise kernels (torch on CPU)
+    def _add_rmsnorm(self, x, residual, weight, out, residual_out):
+        if not self.cpu:
+            ops.add_rmsnorm(x, residual, weight, out, residual_out, self.cfg.eps)
+            return
+        z = x.float() if residual is None else x.float() + residual.float()
+        if residual_out is not None:
+            residual_out.copy_(z.to(residual_out.dtype))      # the norm below uses the unrounded sum, like the kernel
+        out.copy_((z * torch.rsqrt(z.pow(2).mean(-1, keepdim=True) + self.cfg.eps) * weight.float()).to(out.dtype))
+
+    def _rope(self):
+        cfg, D = self.cfg, self.cfg.head_dim
+        if not self.cpu:
+            ops.rope_rows(self.qkv, self.Hq, self.Hkv, D, 0, cfg.rope_theta)
+            return
+        half, nh = D // 2, self.Hq + self.Hkv
+        inv = cfg.rope_theta ** (-2.0 * torch.arange(half, dtype=torch.float32) / D)
+        ang = torch.arange(self.T, dtype=torch.float32)[:, None] * inv[None]
+        cos, sin = ang.cos()[:, None], ang.sin()[:, None]
+        v = self.qkv.view(self.T, self.Hq + 2 * self.Hkv, D)
+        a, b = v[:, :nh, :half].float(), v[:, :nh, half:].float()
+        v[:, :nh, :half] = (a * cos - b * sin).to(v.dtype)
+        v[:, :nh, half:] = (b * cos + a * sin).to(v.dtype)
+
+    def _silu_mul(self):
+        if not self.cpu:
+            ops.silu_mul(self.gu, self.act)
+            return
+        g, u = self.gu[:, :self.F].float(), self.gu[:, self.F:].float()
+        self.act.copy_((F_.silu(g) * u).to(self.act.dtype))
+
     def _attention(self):
         cfg, D, T = self.cfg, self.cfg.head_dim, self.T
-        ops.rope_rows(self.qkv, self.Hq, self.Hkv, D, 0, cfg.rope_theta)
+        self._rope()
         q = self.qkv[:, :self.Hq * D].view(T, self.Hq, D).permute(1, 0, 2).unsqueeze(0)
         k = self.qkv[:, self.Hq * D:(self.Hq + self.Hkv) * D].view(T, self.Hkv, D).permute(1, 0, 2).unsqueeze(0)
         v = self.qkv[:, (self.Hq + self.Hkv) * D:].view(T, self.Hkv, D).permute(1, 0, 2).unsqueeze(0)
@@ -129,19 +167,18 @@ class LlamaSPPrefill:
     # ------------------------------------------------------------------ forward
     def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
         """x_shard: this rank's [T / world, hidden] rows of the residual stream; returns the same rows after all layers."""
-        eps = self.cfg.eps
         res = x_shard.clone()
-        ops.add_rmsnorm(res, None, self.layers[0]["norm1"], self.h, None, eps)
+        self._add_rmsnorm(res, None, self.layers[0]["norm1"], self.h, None)
         for li, l in enumerate(self.layers):
             self._col(self.h, l["wqkv"], self.qkv)
             self._attention()
             self._row(self.attn, l["wo"], self.part)
-            ops.add_rmsnorm(self.part, res, l["norm2"], self.h, res, eps)       # res += o_proj; h = norm(res)
+            self._add_rmsnorm(self.part, res, l["norm2"], self.h, res)          # res += o_proj; h = norm(res)
             self._col(self.h, l["wgu"], self.gu)
-            ops.silu_mul(self.gu, self.act)
+            self._silu_mul()
             self._row(self.act, l["wd"], self.part)
             if li + 1 < self.L:
-                ops.add_rmsnorm(self.part, res, self.layers[li + 1]["norm1"], self.h, res, eps)
+                self._add_rmsnorm(self.part, res, self.layers[li + 1]["norm1"], self.h, res)
             else:
                 res.add_(self.part)
         return res

@@ -92,6 +92,45 @@ def test_gloo_world2_all_collectives():
             assert text == "", f"rank {r}: {text}"
 
 
+def _sp_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from penny_b200.models.llama_sp import LlamaSPPrefill
+    from penny_b200.models.llama_tp import LlamaConfig
+    from penny_b200.parallel.cpu_backend import CpuCommunicator
+    verdict = ""
+    try:
+        cfg = LlamaConfig(hidden=256, layers=2, heads=4, kv_heads=2, head_dim=128, ffn=512, vocab=512)
+        T, L = 32, 2
+        x = torch.randn(T, cfg.hidden, generator=torch.Generator().manual_seed(3)).bfloat16()
+        want = LlamaSPPrefill.reference_forward(cfg, x, L, seed=4)
+        comm = CpuCommunicator()
+        m = LlamaSPPrefill(cfg, comm=comm, rank=rank, world=world, tokens=T, layers=L, seed=4, device="cpu")
+        rows = T // world
+        got = m.forward(x[rank * rows:(rank + 1) * rows].contiguous()).float()
+        ref = want[rank * rows:(rank + 1) * rows]
+        rel = ((got - ref).norm() / ref.norm()).item()
+        if not rel < 3e-2:
+            verdict = f"relative error {rel}"
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        verdict = "exception: " + traceback.format_exc()[-800:]
+    with open(os.path.join(out_dir, f"r{rank}.txt"), "w") as f:
+        f.write(verdict)
+    dist.destroy_process_group()
+
+
+def test_sp_prefill_partitioning_on_gloo():
+    """The sequence-parallel prefill model on two CPU ranks (torch ops, gloo collectives): the
+    weight slicing, the sequence sharding and the layer wiring against the fp32 one-device oracle."""
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_sp_worker, args=(2, _free_port(), d), nprocs=2, join=True)
+        for r in range(2):
+            text = open(os.path.join(d, f"r{r}.txt")).read().strip()
+            assert text == "", f"rank {r}: {text}"
+
+
 def _dead_rank_worker(rank, world, port, out_dir):
     """Failure detection on the host: rank 1 raises before joining the collective;
     rank 0's collective must end with an error within the group timeout."""
