@@ -92,3 +92,59 @@ def test_penny_config_env_and_overrides(monkeypatch):
         PennyConfig.from_env(heap_mode="nvshmem")
     with pytest.raises(ValueError):
         PennyConfig.from_env(vllm_algo="3stage")
+
+
+def test_custom_allreduce_dispatch_logic(monkeypatch):
+    """The host-side decisions of the drop-in CustomAllreduce, with the native calls
+    replaced by a recorder: which inputs it serves, staging vs registered buffers,
+    the warm-up pass inside capture(), and None as the "use your fallback" answer
+    (same contract as the reference, penny/custom_all_reduce.py:214-267)."""
+    import torch
+    import penny_b200.parallel.custom_all_reduce as car_mod
+    calls = []
+
+    class FakeOps:
+        def all_reduce(self, ptr, inp, out, reg, size):
+            calls.append(("all_reduce", reg, size))
+
+        def reduce_scatter(self, ptr, inp, out, reg, size):
+            calls.append(("reduce_scatter", reg, size))
+
+        def all_gather(self, ptr, inp, out, reg, size):
+            calls.append(("all_gather", reg, size))
+
+        def get_graph_buffer_ipc_meta(self, ptr):
+            raise AssertionError("not reached: the object is disabled when capture() exits in this test")
+
+    monkeypatch.setattr(car_mod, "ops", FakeOps())
+    car = car_mod.CustomAllreduce.__new__(car_mod.CustomAllreduce)
+    car._IS_CAPTURING, car.disabled, car._ptr, car._comm = False, False, 1234, None
+    car.rank, car.world_size, car.fully_connected, car.max_size = 1, 4, True, 1 << 20
+    car.buffer_ptrs = [10, 11, 12, 13]
+
+    ok = torch.zeros(4096, dtype=torch.bfloat16)
+    assert car.should_custom_ar(ok)
+    assert not car.should_custom_ar(torch.zeros(7, dtype=torch.bfloat16))          # not a multiple of 16 bytes
+    assert not car.should_custom_ar(torch.zeros(1 << 20, dtype=torch.bfloat16))    # 2 MiB >= max_size
+    assert not car.should_custom_ar(torch.zeros(64, 64)[:, ::2])                   # not weakly contiguous
+    assert car.should_custom_ar(torch.zeros(64, 64)[8:])                           # a dense tail of a storage is fine
+
+    # eager: staged through this rank's registered buffer
+    out = car.custom_all_reduce(ok)
+    assert out is not None and out.shape == ok.shape and calls[-1] == ("all_reduce", 11, 1 << 20)
+    assert car.custom_all_reduce(torch.zeros(7, dtype=torch.bfloat16)) is None     # caller falls back
+    # inside capture() but not capturing a graph yet (the warm-up run): no communication
+    n = len(calls)
+    car._IS_CAPTURING = True
+    monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: False)
+    warm = car.custom_all_gather(ok)
+    assert len(calls) == n and warm.numel() == ok.numel() * 4
+    # while the graph is being captured: the buffer itself is registered later, no staging copy
+    monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: True)
+    car.custom_reduce_scatter(ok)
+    assert calls[-1] == ("reduce_scatter", 0, 0)
+    car._IS_CAPTURING = False
+    # disabled object: every entry point answers None
+    car.disabled = True
+    assert car.custom_all_reduce(ok) is None and car.custom_all_gather(ok) is None
+    car._ptr = 0  # nothing to dispose in __del__
