@@ -148,3 +148,50 @@ def test_custom_allreduce_dispatch_logic(monkeypatch):
     car.disabled = True
     assert car.custom_all_reduce(ok) is None and car.custom_all_gather(ok) is None
     car._ptr = 0  # nothing to dispose in __del__
+
+
+def test_bench_clock_sampler_against_fake_nvml(monkeypatch):
+    """bench.py samples SM clocks and throttle reasons during the timed region through
+    NVML (read-only queries).  Checked here against a fake NVML: the median clock, the
+    decoding of the reason bit mask, and the look-up of the GPU by UUID."""
+    import importlib.util
+    import time
+    import types
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    monkeypatch.setattr(sys, "argv", ["bench.py"])
+    spec.loader.exec_module(bench)
+
+    fake = types.ModuleType("pynvml")
+    fake.NVML_CLOCK_SM = 1
+    fake.NVMLError = RuntimeError
+    seen = {"uuid": None, "polls": 0}
+    fake.nvmlInit = lambda: None
+
+    def by_uuid(u):
+        seen["uuid"] = u
+        return "handle"
+    fake.nvmlDeviceGetHandleByUUID = by_uuid
+    fake.nvmlDeviceGetHandleByIndex = lambda i: "handle"
+    fake.nvmlDeviceGetMaxClockInfo = lambda h, k: 1965
+
+    def clock(h, k):
+        seen["polls"] += 1
+        return 1965 if seen["polls"] % 4 else 1700
+    fake.nvmlDeviceGetClockInfo = clock
+    fake.nvmlDeviceGetCurrentClocksThrottleReasons = lambda h: 0x4 | 0x1    # sw_power_cap | gpu_idle (ignored)
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+
+    s = bench.ClockSampler(3, "abcd-ef").prepare()
+    s.start()
+    time.sleep(0.08)
+    rec = s.stop()
+    assert seen["uuid"] == b"GPU-abcd-ef"
+    assert rec["source"] == "nvml" and rec["samples"] >= 3
+    assert rec["sm_mhz"] == 1965.0 and rec["sm_max_mhz"] == 1965.0
+    assert rec["reasons"] == ["sw_power_cap"]
+    fake.nvmlDeviceGetCurrentClocksThrottleReasons = lambda h: 0x40 | 0x8
+    s2 = bench.ClockSampler(0).prepare()
+    s2.start()
+    time.sleep(0.03)
+    assert s2.stop()["reasons"] == ["hw_slowdown", "hw_thermal_slowdown"]
