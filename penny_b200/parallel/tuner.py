@@ -93,3 +93,28 @@ class Tuner:
         if algo.startswith("nvls") and not has_multicast:
             algo = "oneshot" if nbytes <= (256 << 10) else "twoshot"
         return algo
+
+
+def _main(argv=None) -> int:
+    """python -m penny_b200.parallel.tuner sweep.jsonl [--out cache.json] [--dtype bf16]
+
+    Turns the JSON lines of `extra/benchmark_allreduce.py --out sweep.jsonl` into the cached table."""
+    import argparse
+    ap = argparse.ArgumentParser(prog="python -m penny_b200.parallel.tuner", description=_main.__doc__)
+    ap.add_argument("sweep", help="JSON-lines file written by extra/benchmark_allreduce.py --out")
+    ap.add_argument("--out", default=None, help=f"cache file (default: PENNY_TUNER_CACHE or {DEFAULT_CACHE})")
+    ap.add_argument("--dtype", default=None, help="only use records of this dtype (e.g. bf16)")
+    args = ap.parse_args(argv)
+    t = Tuner.from_sweep(args.sweep, dtype=args.dtype)
+    if not t.table:
+        print("no usable records (op=all_reduce, impl=penny, a named algorithm) in", args.sweep)
+        return 1
+    path = t.save(args.out)
+    for world, rows in sorted(t.table.items(), key=lambda kv: int(kv[0])):
+        print(f"world {world}: " + ", ".join(f"<= {b} B: {a}" if b is not None else f"above: {a}" for b, a in rows))
+    print("written to", path)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(_main())

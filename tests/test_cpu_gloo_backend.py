@@ -179,3 +179,11 @@ def test_tuner_roundtrip(tmp_path):
     saved = t.save(str(tmp_path / "cache.json"))
     assert Tuner.load(saved).table == {k: [tuple(x) for x in v] for k, v in t.table.items()} or Tuner.load(saved).pick(512, 8) == "oneshot_ll"
     assert Tuner().pick(4096, 8) == "oneshot_ll"
+    # the command-line form writes the same cache
+    from penny_b200.parallel.tuner import _main
+    cli_out = tmp_path / "cli_cache.json"
+    assert _main([str(p), "--out", str(cli_out), "--dtype", "bf16"]) == 0
+    assert Tuner.load(str(cli_out)).pick(1 << 19, 8) == "nvls"
+    empty = tmp_path / "empty.jsonl"
+    empty.write_text("")
+    assert _main([str(empty), "--out", str(tmp_path / "none.json")]) == 1
