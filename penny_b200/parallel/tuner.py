@@ -33,6 +33,7 @@ class Tuner:
     def __init__(self, table: Optional[Dict[str, List[Tuple[Optional[int], str]]]] = None, source: str = "builtin"):
         self.table = table or {k: list(v) for k, v in BUILTIN.items()}
         self.source = source
+        self.records = 0
 
     # ---------------------------------------------------------------- building
     @classmethod
@@ -61,7 +62,9 @@ class Tuner:
                 rows.append((size, algo))
         for rows in table.values():
             rows[-1] = (None, rows[-1][1])
-        return cls(table, source=path)
+        t = cls(table, source=path)
+        t.records = len(best)  # (world, size) points the table was built from; 0: the built-in table is in use
+        return t
 
     @classmethod
     def load(cls, path: Optional[str] = None) -> "Tuner":
@@ -106,7 +109,7 @@ def _main(argv=None) -> int:
     ap.add_argument("--dtype", default=None, help="only use records of this dtype (e.g. bf16)")
     args = ap.parse_args(argv)
     t = Tuner.from_sweep(args.sweep, dtype=args.dtype)
-    if not t.table:
+    if not t.records:
         print("no usable records (op=all_reduce, impl=penny, a named algorithm) in", args.sweep)
         return 1
     path = t.save(args.out)
