@@ -14,6 +14,7 @@ import subprocess
 import sys
 
 import setuptools
+import torch
 from torch.utils.cpp_extension import BuildExtension, CUDAExtension
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -80,6 +81,8 @@ if __name__ == "__main__":
                 sources=CPP_SOURCES + CUDA_SOURCES,
                 include_dirs=[os.path.join(ROOT, "csrc")],
                 extra_compile_args={"cxx": CXX_FLAGS, "nvcc": NVCC_FLAGS},
+                # so that `import penny_cpp` finds libc10 / libtorch even when torch was not imported first
+                extra_link_args=["-Wl,-rpath," + os.path.join(os.path.dirname(torch.__file__), "lib")],
             )
         ],
         cmdclass={"build_ext": BuildExtension.with_options(use_ninja=True)},
