@@ -22,6 +22,7 @@ enum Algo : int {
   OP_ALL_GATHER = 17,
   OP_ALL_TO_ALL = 18,
   OP_EXCHANGE = 19,
+  OP_REDUCE_SCATTER_PIPELINED = 20,
 };
 
 inline const char* algo_name(int a) {
@@ -39,6 +40,7 @@ inline const char* algo_name(int a) {
     case OP_ALL_GATHER: return "all_gather";
     case OP_ALL_TO_ALL: return "all_to_all";
     case OP_EXCHANGE: return "exchange";
+    case OP_REDUCE_SCATTER_PIPELINED: return "reduce_scatter_pipelined";
     default: return "auto";
   }
 }

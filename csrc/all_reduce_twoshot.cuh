@@ -176,6 +176,93 @@ struct ReduceScatterPush {
   }
 };
 
+// The same reduce-scatter with the owner's reduction overlapped with the pushes:
+// the shard is cut into up to kRsMaxChunks chunks; a block pushes its slice of
+// chunk k to every peer, raises step k + 1 on its peers' flags and only then
+// waits for step k and reduces chunk k - 1, so the local reduction of one chunk
+// runs while the stores of the next one are still draining over NVLink (the
+// plain variant pays push time + reduce time, which costs it the comparison with
+// NCCL above 8 MiB shards).  Same scratch layout, same flag channel: the flag
+// value only ever grows inside a call (seq * 64 + step, step <= kRsMaxChunks).
+constexpr int kRsMaxChunks = 16;
+
+template <typename T, int NG>
+struct ReduceScatterPipelined {
+  static PK_DEV void body(const CommCtx& c, int rank, const CollArgs& a, const Blk& b, u64 seq,
+                          int& s_abort) {
+    constexpr size_t E = 16 / sizeof(T);
+    const T* in = reinterpret_cast<const T*>(a.in);
+    T* out = reinterpret_cast<T*>(a.out);
+    const size_t shard = a.n / NG;  // elements
+    const size_t SV = ceil_div(shard, E);
+    const size_t base = scratch_half(a.scratch_off, a.scratch_bytes, seq);
+    const size_t stride = (size_t)b.nblocks * b.nthreads;
+    const size_t first = (size_t)b.bid * b.nthreads;
+    // chunks of whole batches: at least four batches per thread and chunk
+    const size_t per_pass = stride * kBatch;
+    size_t passes = ceil_div(SV, per_pass);
+    int chunks = (int)(passes / 4);
+    if (chunks < 1) chunks = 1;
+    if (chunks > kRsMaxChunks) chunks = kRsMaxChunks;
+    const size_t CS = ceil_div(passes, (size_t)chunks) * per_pass;  // vectors per chunk
+    for (int k = 0; k <= chunks; ++k) {
+      if (k < chunks) {
+        const size_t lo = (size_t)k * CS, hi = (lo + CS < SV) ? lo + CS : SV;
+        PK_FOR_THREADS(b, tid) {
+          for (int d = 1; d < NG; ++d) {
+            const int dst = (rank + d) % NG;
+            const T* src = in + (size_t)dst * shard;
+            for (size_t j0 = lo + first + tid; j0 < hi; j0 += kBatch * stride) {
+              V16 x[kBatch];
+#pragma unroll
+              for (int u = 0; u < kBatch; ++u)
+                if (j0 + u * stride < hi) x[u] = load_user_vec<T>(src, j0 + u * stride, shard);
+#pragma unroll
+              for (int u = 0; u < kBatch; ++u)
+                if (j0 + u * stride < hi)
+                  st16(c.heap[dst] + base + ((size_t)rank * SV + j0 + u * stride) * 16, x[u]);
+            }
+          }
+        }
+      }
+      PK_SYNC(b);  // the block's stores of chunk k are issued before anyone signals
+      if (k < chunks) {
+        PK_FOR_THREADS(b, _t) {
+          if (_t < c.world && _t != rank) signal_peer(c, rank, _t, CH_BARRIER, b, flag_value(seq, k + 1));
+        }
+      }
+      if (k >= 1) {
+        PK_FOR_THREADS(b, _t) {
+          if (_t < c.world && _t != rank) {
+            if (!wait_peer(c, rank, _t, CH_BARRIER, b, flag_value(seq, k), ST_TIMEOUT_BARRIER)) s_abort = 1;
+          }
+        }
+        PK_SYNC(b);
+        if (s_abort) return;
+        const size_t lo = (size_t)(k - 1) * CS, hi = (lo + CS < SV) ? lo + CS : SV;
+        PK_FOR_THREADS(b, tid) {
+          const T* own = in + (size_t)rank * shard;
+          for (size_t j = lo + first + tid; j < hi; j += stride) {
+            float acc[E];
+#pragma unroll
+            for (size_t i = 0; i < E; ++i) acc[i] = 0.f;
+#pragma unroll
+            for (int s = 0; s < NG; ++s) {
+              V16 x = (s == rank) ? load_user_vec<T>(own, j, shard)
+                                  : ld16(c.heap[rank] + base + ((size_t)s * SV + j) * 16);
+              unpack_add<T>(x, acc);
+            }
+            store_user_vec<T>(out, j, shard, pack<T>(acc));
+          }
+        }
+      }
+    }
+  }
+  static PK_DEV void run(const CommCtx& c, int rank, const CollArgs& a, const Blk& b) {
+    run_collective<ReduceScatterPipelined<T, NG>, CollArgs>(c, rank, a, b);
+  }
+};
+
 // All-gather.  a.n = elements of one shard; out[r*n .. (r+1)*n) = rank r's input.
 //   direct (output in the heap): start barrier (every peer has entered the call,
 //     so its output buffer is no longer being read by earlier work), push the

@@ -310,7 +310,7 @@ void Communicator::run_all_reduce_once(int algo, int dtype, const void* const* i
 
 void Communicator::reduce_scatter(int dtype, const void* const* in, void* const* out,
                                   size_t n_total, bool nvls, const Tuning& t,
-                                  cudaStream_t stream) {
+                                  cudaStream_t stream, bool pipelined) {
   const int es = dtype_size(dtype);
   if (n_total == 0) return;
   if (n_total % world_ != 0)
@@ -351,7 +351,10 @@ void Communicator::reduce_scatter(int dtype, const void* const* in, void* const*
     a[v].scratch_off = r.off;
     a[v].scratch_bytes = r.bytes;
   }
-  ckrt(launch_reduce_scatter(dtype, ctx_, a, cfg_for(SV, t, stream, 128, 1)), "reduce_scatter");
+  if (pipelined)
+    ckrt(launch_reduce_scatter_pipelined(dtype, ctx_, a, cfg_for(SV, t, stream, 128, 1)), "reduce_scatter (pipelined)");
+  else
+    ckrt(launch_reduce_scatter(dtype, ctx_, a, cfg_for(SV, t, stream, 128, 1)), "reduce_scatter");
 }
 
 void Communicator::all_gather(int dtype, const void* const* in, void* const* out, size_t n_shard,

@@ -76,8 +76,9 @@ class Communicator {
   // in / out: views() pointers each.  n as documented in CollArgs.
   void all_reduce(int algo, int dtype, const void* const* in, void* const* out, size_t n,
                   const Tuning& t, cudaStream_t stream);
+  // pipelined: the push variant that reduces chunk k - 1 while chunk k is on the wire
   void reduce_scatter(int dtype, const void* const* in, void* const* out, size_t n_total, bool nvls,
-                      const Tuning& t, cudaStream_t stream);
+                      const Tuning& t, cudaStream_t stream, bool pipelined = false);
   void all_gather(int dtype, const void* const* in, void* const* out, size_t n_shard, bool nvls,
                   const Tuning& t, cudaStream_t stream);
   void all_to_all(int dtype, const void* const* in, void* const* out, size_t n_chunk,

@@ -67,6 +67,8 @@ cudaError_t launch_all_reduce_twoshot(int dtype, const CommCtx& c, const CollArg
                                       const LaunchCfg& cfg);
 cudaError_t launch_reduce_scatter(int dtype, const CommCtx& c, const CollArgs* a,
                                   const LaunchCfg& cfg);
+cudaError_t launch_reduce_scatter_pipelined(int dtype, const CommCtx& c, const CollArgs* a,
+                                            const LaunchCfg& cfg);
 cudaError_t launch_all_gather(int dtype, const CommCtx& c, const CollArgs* a,
                               const LaunchCfg& cfg);
 cudaError_t launch_all_reduce_ring_simple(int dtype, const CommCtx& c, const CollArgs* a,

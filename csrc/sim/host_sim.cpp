@@ -102,6 +102,7 @@ void run_body(int algo, int world, const CommCtx& c, int rank, const CollArgs& a
       case ALGO_ONESHOT_LL: OneShotLL<T, NG>::run(c, rank, a, b); break;
       case ALGO_TWOSHOT: TwoShot<T, NG>::run(c, rank, a, b); break;
       case OP_REDUCE_SCATTER: ReduceScatterPush<T, NG>::run(c, rank, a, b); break;
+      case OP_REDUCE_SCATTER_PIPELINED: ReduceScatterPipelined<T, NG>::run(c, rank, a, b); break;
       case OP_ALL_GATHER: AllGatherPush<T, NG>::run(c, rank, a, b); break;
       case OP_ALL_TO_ALL: AllToAll<T, NG>::run(c, rank, a, b); break;
       default: break;
@@ -118,7 +119,8 @@ size_t scratch_need(int algo, size_t n, int es, int world, int nnodes, int nbloc
     case ALGO_TWOSHOT: return twoshot_scratch_bytes(n, es, world);
     case ALGO_DOUBLE_RING: return double_ring_scratch_bytes(n, es, world, nnodes, nblocks);
     case ALGO_TREE: return tree_scratch_bytes(n, es, nnodes);
-    case OP_REDUCE_SCATTER: return reduce_scatter_scratch_bytes(n, es, world);
+    case OP_REDUCE_SCATTER:
+    case OP_REDUCE_SCATTER_PIPELINED: return reduce_scatter_scratch_bytes(n, es, world);
     case OP_ALL_GATHER: return all_gather_scratch_bytes(n, es, world);
     case OP_ALL_TO_ALL: return all_to_all_scratch_bytes(n, es, world);
     case OP_EXCHANGE: return exchange_scratch_bytes(n, es);
@@ -129,7 +131,8 @@ size_t scratch_need(int algo, size_t n, int es, int world, int nnodes, int nbloc
 // Elements of the per-rank input / output of one call with size parameter n.
 void io_elems(int algo, size_t n, int world, size_t* in_n, size_t* out_n) {
   switch (algo) {
-    case OP_REDUCE_SCATTER: *in_n = n; *out_n = n / world; break;
+    case OP_REDUCE_SCATTER:
+    case OP_REDUCE_SCATTER_PIPELINED: *in_n = n; *out_n = n / world; break;
     case OP_ALL_GATHER: *in_n = n; *out_n = n * world; break;
     case OP_ALL_TO_ALL: *in_n = n * world; *out_n = n * world; break;
     default: *in_n = n; *out_n = n; break;
@@ -196,8 +199,8 @@ int sim_run_t(int algo, int world, int nblocks, int nthreads, size_t n, int nnod
   Sim<T> s;
   s.algo = algo; s.world = world; s.nblocks = nblocks; s.nthreads = nthreads; s.n = n;
   s.nnodes = nnodes; s.routes = routes; s.iters = iters; s.stall_rank = stall_rank;
-  s.in_place = in_place != 0 && algo != OP_REDUCE_SCATTER && algo != OP_ALL_GATHER &&
-               algo != OP_ALL_TO_ALL;
+  s.in_place = in_place != 0 && algo != OP_REDUCE_SCATTER && algo != OP_REDUCE_SCATTER_PIPELINED &&
+               algo != OP_ALL_GATHER && algo != OP_ALL_TO_ALL;
   if (algo == OP_EXCHANGE) s.in_place = true;
   s.timeout_ns = (uint64_t)timeout_ms * 1000000ull;
   const int es = (int)sizeof(T);
@@ -248,6 +251,7 @@ int sim_run_t(int algo, int world, int nblocks, int nthreads, size_t n, int nnod
           double want = 0.0, mag = 0.0;
           switch (algo) {
             case OP_REDUCE_SCATTER:
+            case OP_REDUCE_SCATTER_PIPELINED:
               for (int q = 0; q < world; ++q) {
                 double v = ref_in[it][q][(size_t)r * out_n + i];
                 want += v; mag += std::fabs(v);

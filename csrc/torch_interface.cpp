@@ -259,17 +259,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
      py::arg("symmetric_in") = false, py::arg("symmetric_out") = false);
 
   m.def("comm_reduce_scatter", [](int64_t h, std::vector<at::Tensor> in, std::vector<at::Tensor> out,
-                                  bool nvls, int blocks, int threads, bool sym_in) {
+                                  bool nvls, int blocks, int threads, bool sym_in, bool pipelined) {
     Communicator* c = as_comm(h);
     TORCH_CHECK(!in.empty() && in[0].numel() == out[0].numel() * c->world(),
                 "penny: reduce_scatter output must hold numel / world elements");
     const at::cuda::OptionalCUDAGuard guard(in[0].device());
     with_views(c, in, out, [&](const void* const* ip, void* const* op) {
       c->reduce_scatter(dtype_of(in[0]), ip, op, (size_t)in[0].numel(), nvls,
-                        make_tuning(blocks, threads, 1, 0, sym_in, false), current_stream());
+                        make_tuning(blocks, threads, 1, 0, sym_in, false), current_stream(), pipelined);
     });
   }, py::arg("comm"), py::arg("inputs"), py::arg("outputs"), py::arg("nvls") = false,
-     py::arg("blocks") = 0, py::arg("threads") = 0, py::arg("symmetric_in") = false);
+     py::arg("blocks") = 0, py::arg("threads") = 0, py::arg("symmetric_in") = false,
+     py::arg("pipelined") = false);
 
   m.def("comm_all_gather", [](int64_t h, std::vector<at::Tensor> in, std::vector<at::Tensor> out,
                               bool nvls, int blocks, int threads, bool sym_out) {

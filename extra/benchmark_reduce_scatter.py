@@ -8,6 +8,8 @@ and the drop-in CustomAllreduce.reduce_scatter (<= 8 MiB inputs).  Bus bandwidth
 = (n-1)/n * input_bytes / t.  Counterpart of the reference's
 extra/benchmark_reduce_scatter.py.
 """
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -44,16 +46,19 @@ def main():
             nccl_us = bench_device(lambda: dist.reduce_scatter_tensor(ref, buf), args.warmup, args.num_tests)["median_us"]
             rec.add(op="reduce_scatter", impl="nccl", world=world, dtype=args.dtype, shard_bytes=shard_bytes,
                     t_us=round(nccl_us, 2), busbw_gbs=round(bus_bandwidth_gbs("reduce_scatter", total, world, nccl_us), 2))
-        variants = [("push", False)]
+        variants = [("push", False, False)]
+        if os.environ.get("PENNY_RS_PIPELINED", "0") == "1":
+            variants.append(("push_pipelined", False, True))   # opt-in until it has been timed on hardware
         if comm.has_multicast and shard_bytes % 16 == 0:
-            variants.append(("nvls", True))
+            variants.append(("nvls", True, False))
         out = torch.empty(shard, device="cuda", dtype=dtype)
-        for name, nvls in variants:
-            comm.reduce_scatter(x, out=out, nvls=nvls)
+        for name, nvls, pipe in variants:
+            comm.reduce_scatter(x, out=out, nvls=nvls, pipelined=pipe)
             comm.check()
             if not torch.allclose(out.float(), ref.float(), atol=args.atol, rtol=args.rtol):
                 raise SystemExit(f"rank {rank}: reduce_scatter/{name} @ {shard_bytes} B differs from NCCL")
-            t = bench_device(lambda: comm.reduce_scatter(x, out=out, nvls=nvls), args.warmup, args.num_tests)["median_us"]
+            t = bench_device(lambda: comm.reduce_scatter(x, out=out, nvls=nvls, pipelined=pipe), args.warmup,
+                             args.num_tests)["median_us"]
             bw = bus_bandwidth_gbs("reduce_scatter", total, world, t)
             rec.add(op="reduce_scatter", impl="penny", algo=name, world=world, dtype=args.dtype,
                     shard_bytes=shard_bytes, t_us=round(t, 2), busbw_gbs=round(bw, 2),

@@ -192,13 +192,15 @@ class Communicator:
         return self._ret(outs)
 
     def reduce_scatter(self, inp: TensorOrList, out: Optional[TensorOrList] = None, nvls: bool = False,
-                       blocks: int = 0, threads: int = 0):
+                       blocks: int = 0, threads: int = 0, pipelined: bool = False):
+        """out[numel / world] = this rank's shard of the sum.  pipelined=True: the push
+        variant that reduces one chunk while the next is on the wire (large shards)."""
         ins = self._as_list(inp)
         if out is None:
             outs = [torch.empty(x.numel() // self.world_size, dtype=x.dtype, device=x.device) for x in ins]
         else:
             outs = self._as_list(out)
-        ops.comm_reduce_scatter(self._h, ins, outs, nvls, blocks, threads, self.is_symmetric(ins))
+        ops.comm_reduce_scatter(self._h, ins, outs, nvls, blocks, threads, self.is_symmetric(ins), pipelined)
         return self._ret(outs)
 
     def all_gather(self, inp: TensorOrList, out: Optional[TensorOrList] = None, nvls: bool = False,

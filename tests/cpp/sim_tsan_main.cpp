@@ -14,15 +14,15 @@
 
 int main() {
   // ids as in csrc/algos.h and the simulator's extra collectives
-  const int algos[] = {0, 1, 2, 3, 4, 5, 7, 16, 17, 18, 19};
+  const int algos[] = {0, 1, 2, 3, 4, 5, 7, 16, 17, 18, 19, 20};
   int bad = 0;
   for (int algo : algos)
     for (int world : {2, 4})
       for (int dtype : {0, 2})                       // fp32, bf16
-        for (unsigned long long n : {1ull, 1023ull, 1536ull}) {
+        for (unsigned long long n : {1ull, 1023ull, 1536ull, 40000ull}) {
           const int nnodes = ((algo == 4 || algo == 5) && world == 4) ? 2 : 1;
           // the partitioned collectives take a per-rank count that world must divide
-          const unsigned long long nn = (algo >= 16 && algo <= 18) ? n * world : n;
+          const unsigned long long nn = ((algo >= 16 && algo <= 18) || algo == 20) ? n * world : n;
           double err = 0.0;
           const int rc = penny_sim_run(algo, dtype, world, /*nblocks*/ 2, /*nthreads*/ 4, nn, nnodes,
                                        /*routes*/ 2, /*iters*/ 3, /*seed*/ 7u, /*stall_rank*/ -1,

@@ -193,6 +193,23 @@ def test_bounded_wait_reports_status(comms):
     torch.testing.assert_close(outs[0], ins[0] + ins[1])
 
 
+@pytest.mark.skipif(__import__("os").environ.get("PENNY_TEST_UNVERIFIED") != "1",
+                    reason="pipelined reduce-scatter: proven on the host simulator (incl. Thread/AddressSanitizer), "
+                           "not yet run on a GPU; set PENNY_TEST_UNVERIFIED=1")
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_reduce_scatter_pipelined(comms, world):
+    comm = comms(world)
+    for dtype in (torch.float32, torch.bfloat16):
+        for shard in (1, 1023, 4096, 300000):
+            ins = make_inputs(world, shard * world, dtype, seed=shard)
+            total = torch.stack([x.float() for x in ins]).sum(0)
+            for _ in range(2):  # both scratch halves
+                outs = comm.reduce_scatter(ins, pipelined=True)
+                comm.check()
+                for r in range(world):
+                    torch.testing.assert_close(outs[r].float(), total[r * shard:(r + 1) * shard], **TOL[dtype])
+
+
 def test_poisoned_scratch_never_reaches_a_result():
     """debug_poison: every check() overwrites all scratch regions with 0xFF bytes
     (NaN in every float format).  A protocol that consumed scratch it was not sent
