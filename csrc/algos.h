@@ -23,6 +23,7 @@ enum Algo : int {
   OP_ALL_TO_ALL = 18,
   OP_EXCHANGE = 19,
   OP_REDUCE_SCATTER_PIPELINED = 20,
+  OP_ALL_TO_ALL_PIPELINED = 21,
 };
 
 inline const char* algo_name(int a) {
@@ -41,6 +42,7 @@ inline const char* algo_name(int a) {
     case OP_ALL_TO_ALL: return "all_to_all";
     case OP_EXCHANGE: return "exchange";
     case OP_REDUCE_SCATTER_PIPELINED: return "reduce_scatter_pipelined";
+    case OP_ALL_TO_ALL_PIPELINED: return "all_to_all_pipelined";
     default: return "auto";
   }
 }

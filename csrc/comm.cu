@@ -402,7 +402,7 @@ void Communicator::all_gather(int dtype, const void* const* in, void* const* out
 }
 
 void Communicator::all_to_all(int dtype, const void* const* in, void* const* out, size_t n_chunk,
-                              const Tuning& t, cudaStream_t stream) {
+                              const Tuning& t, cudaStream_t stream, bool pipelined) {
   const int es = dtype_size(dtype);
   if (n_chunk == 0) return;
   if (world_ == 1) {
@@ -432,8 +432,12 @@ void Communicator::all_to_all(int dtype, const void* const* in, void* const* out
       a[v].scratch_bytes = r.bytes;
     }
   }
-  ckrt(launch_all_to_all(dtype, ctx_, a, cfg_for(vecs_for(n_chunk, es), t, stream, 128, 1)),
-       "all_to_all");
+  if (pipelined && a[0].out_heap_off == kNotInHeap)
+    ckrt(launch_all_to_all_pipelined(dtype, ctx_, a, cfg_for(vecs_for(n_chunk, es), t, stream, 128, 1)),
+         "all_to_all (pipelined)");
+  else
+    ckrt(launch_all_to_all(dtype, ctx_, a, cfg_for(vecs_for(n_chunk, es), t, stream, 128, 1)),
+         "all_to_all");
 }
 
 void Communicator::exchange(int dtype, void* const* buf, size_t n, const int* peers,

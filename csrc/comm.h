@@ -81,8 +81,9 @@ class Communicator {
                       const Tuning& t, cudaStream_t stream, bool pipelined = false);
   void all_gather(int dtype, const void* const* in, void* const* out, size_t n_shard, bool nvls,
                   const Tuning& t, cudaStream_t stream);
+  // pipelined (scratch path only): piece k - 1 is copied out while piece k is on the wire
   void all_to_all(int dtype, const void* const* in, void* const* out, size_t n_chunk,
-                  const Tuning& t, cudaStream_t stream);
+                  const Tuning& t, cudaStream_t stream, bool pipelined = false);
   void exchange(int dtype, void* const* buf, size_t n, const int* peers, const Tuning& t,
                 cudaStream_t stream);
   // proto: FusedProto.  Pointer arrays have views() entries.

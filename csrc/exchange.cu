@@ -21,6 +21,15 @@ cudaError_t launch_all_to_all(int dtype, const CommCtx& c, const CollArgs* a,
   return rc;
 }
 
+cudaError_t launch_all_to_all_pipelined(int dtype, const CommCtx& c, const CollArgs* a,
+                                        const LaunchCfg& cfg) {
+  cudaError_t rc = cudaErrorInvalidValue;
+  PENNY_DISPATCH_DTYPE(dtype, T, PENNY_DISPATCH_WORLD(c.world, NG, return cudaErrorInvalidValue, {
+    rc = launch_body<AllToAllPipelined<T, NG>, CollArgs>(c, a, cfg);
+  }));
+  return rc;
+}
+
 // Waits on a private flag word that nothing ever sets, with the communicator's
 // timeout.  The wait must run out, record ST_TIMEOUT_SELFTEST in the status
 // words and return: this is the only way a timeout is provoked on a GPU.

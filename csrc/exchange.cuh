@@ -136,4 +136,90 @@ struct AllToAll {
   }
 };
 
+// All-to-all through scratch with the copy-out overlapped with the pushes: the
+// per-peer chunk is cut into up to kA2aMaxChunks pieces; a block pushes its slice
+// of piece k to every peer, raises step k + 1 and only then waits for step k and
+// copies piece k - 1 from its scratch slots to the output, so one piece is being
+// copied out while the next is on the wire (the plain variant pushes everything,
+// waits once, then copies everything).  Same scratch layout as AllToAll.
+constexpr int kA2aMaxChunks = 16;
+
+template <typename T, int NG>
+struct AllToAllPipelined {
+  static PK_DEV void body(const CommCtx& c, int rank, const CollArgs& a, const Blk& b, u64 seq,
+                          int& s_abort) {
+    constexpr size_t E = 16 / sizeof(T);
+    const T* in = reinterpret_cast<const T*>(a.in);
+    T* out = reinterpret_cast<T*>(a.out);
+    const size_t CV = ceil_div(a.n, E);
+    const size_t stride = (size_t)b.nblocks * b.nthreads;
+    const size_t first = (size_t)b.bid * b.nthreads;
+    const size_t base = scratch_half(a.scratch_off, a.scratch_bytes, seq);
+    const size_t per_pass = stride * kBatch;
+    const size_t passes = ceil_div(CV, per_pass);
+    int chunks = (int)(passes / 4);
+    if (chunks < 1) chunks = 1;
+    if (chunks > kA2aMaxChunks) chunks = kA2aMaxChunks;
+    const size_t CS = ceil_div(passes, (size_t)chunks) * per_pass;  // vectors per piece
+    for (int k = 0; k <= chunks; ++k) {
+      if (k < chunks) {
+        const size_t lo = (size_t)k * CS, hi = (lo + CS < CV) ? lo + CS : CV;
+        PK_FOR_THREADS(b, tid) {
+          for (int d = 0; d < NG; ++d) {
+            const int p = (rank + d) % NG;
+            for (size_t j0 = lo + first + tid; j0 < hi; j0 += kBatch * stride) {
+              V16 x[kBatch];
+#pragma unroll
+              for (int u = 0; u < kBatch; ++u)
+                if (j0 + u * stride < hi) x[u] = load_user_vec<T>(in + (size_t)p * a.n, j0 + u * stride, a.n);
+#pragma unroll
+              for (int u = 0; u < kBatch; ++u) {
+                const size_t j = j0 + u * stride;
+                if (j >= hi) continue;
+                if (p == rank)
+                  store_user_vec<T>(out + (size_t)rank * a.n, j, a.n, x[u]);
+                else
+                  st16(c.heap[p] + base + ((size_t)rank * CV + j) * 16, x[u]);
+              }
+            }
+          }
+        }
+      }
+      PK_SYNC(b);  // the block's stores of piece k are issued before anyone signals
+      if (k < chunks) {
+        PK_FOR_THREADS(b, _t) {
+          if (_t < c.world && _t != rank) signal_peer(c, rank, _t, CH_BARRIER, b, flag_value(seq, k + 1));
+        }
+      }
+      if (k >= 1) {
+        PK_FOR_THREADS(b, _t) {
+          if (_t < c.world && _t != rank) {
+            if (!wait_peer(c, rank, _t, CH_BARRIER, b, flag_value(seq, k), ST_TIMEOUT_BARRIER)) s_abort = 1;
+          }
+        }
+        PK_SYNC(b);
+        if (s_abort) return;
+        const size_t lo = (size_t)(k - 1) * CS, hi = (lo + CS < CV) ? lo + CS : CV;
+        PK_FOR_THREADS(b, tid) {
+          for (int d = 1; d < NG; ++d) {
+            const int s = (rank + d) % NG;
+            for (size_t j0 = lo + first + tid; j0 < hi; j0 += kBatch * stride) {
+              V16 x[kBatch];
+#pragma unroll
+              for (int u = 0; u < kBatch; ++u)
+                if (j0 + u * stride < hi) x[u] = ld16(c.heap[rank] + base + ((size_t)s * CV + j0 + u * stride) * 16);
+#pragma unroll
+              for (int u = 0; u < kBatch; ++u)
+                if (j0 + u * stride < hi) store_user_vec<T>(out + (size_t)s * a.n, j0 + u * stride, a.n, x[u]);
+            }
+          }
+        }
+      }
+    }
+  }
+  static PK_DEV void run(const CommCtx& c, int rank, const CollArgs& a, const Blk& b) {
+    run_collective<AllToAllPipelined<T, NG>, CollArgs>(c, rank, a, b);
+  }
+};
+
 }  // namespace penny

@@ -82,6 +82,8 @@ cudaError_t launch_all_reduce_tree(int dtype, const CommCtx& c, const CollArgs* 
 cudaError_t launch_exchange(int dtype, const CommCtx& c, const CollArgs* a, const LaunchCfg& cfg);
 cudaError_t launch_all_to_all(int dtype, const CommCtx& c, const CollArgs* a,
                               const LaunchCfg& cfg);
+cudaError_t launch_all_to_all_pipelined(int dtype, const CommCtx& c, const CollArgs* a,
+                                        const LaunchCfg& cfg);
 // NVLS (multimem) family: real launches only, c.mc must be set, tensors in the heap.
 cudaError_t launch_all_reduce_nvls(int dtype, bool oneshot, const CommCtx& c, const CollArgs* a,
                                    const LaunchCfg& cfg);

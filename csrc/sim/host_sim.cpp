@@ -105,6 +105,7 @@ void run_body(int algo, int world, const CommCtx& c, int rank, const CollArgs& a
       case OP_REDUCE_SCATTER_PIPELINED: ReduceScatterPipelined<T, NG>::run(c, rank, a, b); break;
       case OP_ALL_GATHER: AllGatherPush<T, NG>::run(c, rank, a, b); break;
       case OP_ALL_TO_ALL: AllToAll<T, NG>::run(c, rank, a, b); break;
+      case OP_ALL_TO_ALL_PIPELINED: AllToAllPipelined<T, NG>::run(c, rank, a, b); break;
       default: break;
     }
   });
@@ -122,7 +123,8 @@ size_t scratch_need(int algo, size_t n, int es, int world, int nnodes, int nbloc
     case OP_REDUCE_SCATTER:
     case OP_REDUCE_SCATTER_PIPELINED: return reduce_scatter_scratch_bytes(n, es, world);
     case OP_ALL_GATHER: return all_gather_scratch_bytes(n, es, world);
-    case OP_ALL_TO_ALL: return all_to_all_scratch_bytes(n, es, world);
+    case OP_ALL_TO_ALL:
+    case OP_ALL_TO_ALL_PIPELINED: return all_to_all_scratch_bytes(n, es, world);
     case OP_EXCHANGE: return exchange_scratch_bytes(n, es);
     default: return 0;
   }
@@ -134,7 +136,8 @@ void io_elems(int algo, size_t n, int world, size_t* in_n, size_t* out_n) {
     case OP_REDUCE_SCATTER:
     case OP_REDUCE_SCATTER_PIPELINED: *in_n = n; *out_n = n / world; break;
     case OP_ALL_GATHER: *in_n = n; *out_n = n * world; break;
-    case OP_ALL_TO_ALL: *in_n = n * world; *out_n = n * world; break;
+    case OP_ALL_TO_ALL:
+    case OP_ALL_TO_ALL_PIPELINED: *in_n = n * world; *out_n = n * world; break;
     default: *in_n = n; *out_n = n; break;
   }
 }
@@ -200,7 +203,7 @@ int sim_run_t(int algo, int world, int nblocks, int nthreads, size_t n, int nnod
   s.algo = algo; s.world = world; s.nblocks = nblocks; s.nthreads = nthreads; s.n = n;
   s.nnodes = nnodes; s.routes = routes; s.iters = iters; s.stall_rank = stall_rank;
   s.in_place = in_place != 0 && algo != OP_REDUCE_SCATTER && algo != OP_REDUCE_SCATTER_PIPELINED &&
-               algo != OP_ALL_GATHER && algo != OP_ALL_TO_ALL;
+               algo != OP_ALL_GATHER && algo != OP_ALL_TO_ALL && algo != OP_ALL_TO_ALL_PIPELINED;
   if (algo == OP_EXCHANGE) s.in_place = true;
   s.timeout_ns = (uint64_t)timeout_ms * 1000000ull;
   const int es = (int)sizeof(T);
@@ -261,6 +264,7 @@ int sim_run_t(int algo, int world, int nblocks, int nthreads, size_t n, int nnod
               want = ref_in[it][i / n][i % n]; mag = std::fabs(want);
               break;
             case OP_ALL_TO_ALL:
+            case OP_ALL_TO_ALL_PIPELINED:
               want = ref_in[it][i / n][(size_t)r * n + i % n]; mag = std::fabs(want);
               break;
             case OP_EXCHANGE: {

@@ -286,17 +286,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
      py::arg("blocks") = 0, py::arg("threads") = 0, py::arg("symmetric_out") = false);
 
   m.def("comm_all_to_all", [](int64_t h, std::vector<at::Tensor> in, std::vector<at::Tensor> out,
-                              int blocks, int threads, bool sym_out) {
+                              int blocks, int threads, bool sym_out, bool pipelined) {
     Communicator* c = as_comm(h);
     TORCH_CHECK(!in.empty() && out[0].numel() == in[0].numel() && in[0].numel() % c->world() == 0,
                 "penny: all_to_all needs equal chunks");
     const at::cuda::OptionalCUDAGuard guard(in[0].device());
     with_views(c, in, out, [&](const void* const* ip, void* const* op) {
       c->all_to_all(dtype_of(in[0]), ip, op, (size_t)in[0].numel() / c->world(),
-                    make_tuning(blocks, threads, 1, 0, false, sym_out), current_stream());
+                    make_tuning(blocks, threads, 1, 0, false, sym_out), current_stream(), pipelined);
     });
   }, py::arg("comm"), py::arg("inputs"), py::arg("outputs"), py::arg("blocks") = 0,
-     py::arg("threads") = 0, py::arg("symmetric_out") = false);
+     py::arg("threads") = 0, py::arg("symmetric_out") = false, py::arg("pipelined") = false);
 
   m.def("comm_exchange", [](int64_t h, std::vector<at::Tensor> bufs, std::vector<int> peers,
                             int blocks, int threads) {

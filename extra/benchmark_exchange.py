@@ -8,6 +8,8 @@ reference's extra/benchmark_exchange.py:54-60.  The swap is checked bit-exactly
 against batch_isend_irecv.  `--all-to-all` adds the N-way exchange with equal
 per-peer chunks of the same size against all_to_all_single.
 """
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -71,6 +73,16 @@ def main():
                     t_us=round(t, 2), egress_gbs=round(sent / t / 1e3, 2),
                     frac_nvlink=round(sent / t / 1e3 / NVLINK_GBS, 4),
                     nccl_us=round(t_nccl, 2) if t_nccl else None, vs_nccl=round(t_nccl / t, 3) if t_nccl else None)
+            if os.environ.get("PENNY_A2A_PIPELINED", "0") == "1":   # opt-in until it has been timed on hardware
+                out2 = comm.all_to_all(xs, pipelined=True)
+                comm.check()
+                if not torch.equal(out2, ref):
+                    raise SystemExit(f"rank {rank}: pipelined all_to_all @ {nbytes} B per peer differs from NCCL")
+                t = bench_device(lambda: comm.all_to_all(xs, out=out2, pipelined=True), args.warmup,
+                                 args.num_tests)["median_us"]
+                rec.add(op="all_to_all", impl="penny", algo="pipelined", world=world, dtype=args.dtype,
+                        bytes_per_peer=nbytes, t_us=round(t, 2), egress_gbs=round(sent / t / 1e3, 2),
+                        vs_nccl=round(t_nccl / t, 3) if t_nccl else None)
     comm.check()
     rec.close()
     shutdown()

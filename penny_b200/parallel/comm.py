@@ -214,10 +214,12 @@ class Communicator:
         return self._ret(outs)
 
     def all_to_all(self, inp: TensorOrList, out: Optional[TensorOrList] = None, blocks: int = 0,
-                   threads: int = 0):
+                   threads: int = 0, pipelined: bool = False):
+        """out[s * n : (s + 1) * n] = rank s's in[rank * n : (rank + 1) * n].  pipelined=True (ordinary
+        output tensors only): one piece is copied out of scratch while the next is on the wire."""
         ins = self._as_list(inp)
         outs = self._as_list(out) if out is not None else [torch.empty_like(x) for x in ins]
-        ops.comm_all_to_all(self._h, ins, outs, blocks, threads, self.is_symmetric(outs))
+        ops.comm_all_to_all(self._h, ins, outs, blocks, threads, self.is_symmetric(outs), pipelined)
         return self._ret(outs)
 
     def exchange(self, buf: TensorOrList, peer: Union[int, Sequence[int]], blocks: int = 0, threads: int = 0):

@@ -30,12 +30,13 @@ def test_all_reduce_protocols(algo, world, dtype):
             assert err <= 1.0, (algo, world, n, nnodes, err)
 
 
-@pytest.mark.parametrize("op", ["reduce_scatter", "reduce_scatter_pipelined", "all_gather", "all_to_all", "exchange"])
+@pytest.mark.parametrize("op", ["reduce_scatter", "reduce_scatter_pipelined", "all_gather", "all_to_all",
+                                "all_to_all_pipelined", "exchange"])
 @pytest.mark.parametrize("world", [2, 4, 6, 8])
 def test_other_collectives(op, world):
     for dtype in ("float32", "float16", "bfloat16"):
         # 50000 per shard: the pipelined reduce-scatter runs its full 16 chunks (3 blocks x 8 threads)
-        for n in (1, 1023, 4096) + ((50000,) if op == "reduce_scatter_pipelined" else ()):
+        for n in (1, 1023, 4096) + ((50000,) if op.endswith("_pipelined") else ()):
             size = n * world if op.startswith("reduce_scatter") else n
             failed, err, status = schedule.simulate(op, dtype, world, 3, 8, size, iters=5)
             assert failed == 0 and err <= 1.0, (op, world, dtype, n, err, status)
@@ -50,13 +51,13 @@ def test_one_mb_two_ranks():
 
 
 @pytest.mark.parametrize("algo", ["oneshot", "oneshot_ll", "twoshot", "ring_standard", "tree", "double_ring",
-                                  "reduce_scatter_pipelined"])
+                                  "reduce_scatter_pipelined", "all_to_all_pipelined"])
 def test_missing_rank_times_out_cleanly(algo):
     """Fault injection on the host: rank 1 never joins.  Every other rank must give
     up after the timeout, record who it waited for, and return."""
     world = 4
     nnodes = 2 if algo in ("tree", "double_ring") else 1
-    blocks = 3 if algo == "reduce_scatter_pipelined" else grid_for(algo, world, nnodes, 1)
+    blocks = 3 if algo.endswith("_pipelined") else grid_for(algo, world, nnodes, 1)
     failed, err, status = schedule.simulate(algo, "float32", world, blocks, 8, 4096 * world,
                                             nnodes=nnodes, iters=1, stall_rank=1, timeout_ms=150)
     assert failed >= 1

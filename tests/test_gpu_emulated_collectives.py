@@ -210,6 +210,23 @@ def test_reduce_scatter_pipelined(comms, world):
                     torch.testing.assert_close(outs[r].float(), total[r * shard:(r + 1) * shard], **TOL[dtype])
 
 
+@pytest.mark.skipif(__import__("os").environ.get("PENNY_TEST_UNVERIFIED") != "1",
+                    reason="pipelined all-to-all: proven on the host simulator (incl. Thread/AddressSanitizer), "
+                           "not yet run on a GPU; set PENNY_TEST_UNVERIFIED=1")
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_all_to_all_pipelined(comms, world):
+    comm = comms(world)
+    for dtype in (torch.float32, torch.bfloat16):
+        for n in (1, 1023, 4096, 200000):
+            ins = make_inputs(world, n * world, dtype, seed=n)
+            for _ in range(2):  # both scratch halves
+                outs = comm.all_to_all(ins, pipelined=True)
+                comm.check()
+                for r in range(world):
+                    want = torch.cat([ins[s][r * n:(r + 1) * n] for s in range(world)])
+                    assert torch.equal(outs[r], want), (world, dtype, n, r)
+
+
 def test_poisoned_scratch_never_reaches_a_result():
     """debug_poison: every check() overwrites all scratch regions with 0xFF bytes
     (NaN in every float format).  A protocol that consumed scratch it was not sent
