@@ -245,6 +245,12 @@ void Communicator::run_all_reduce_once(int algo, int dtype, const void* const* i
       rc = launch_all_reduce_twoshot(dtype, ctx_, a, cfg_for(ceil_div(V, world_), t, stream, 128, 1));
       break;
     }
+    case ALGO_TWOSHOT_PIPELINED: {
+      // always through the gather area (the variant the host simulator has proven)
+      set_scratch(ensure(scratch_, twoshot_scratch_bytes(n, es, world_), "two-shot"));
+      rc = launch_all_reduce_twoshot_pipelined(dtype, ctx_, a, cfg_for(ceil_div(V, world_), t, stream, 128, 1));
+      break;
+    }
     case ALGO_RING_SIMPLE: {
       set_scratch(ensure(scratch_, ring_simple_scratch_bytes(n, es, world_), "ring"));
       rc = launch_all_reduce_ring_simple(dtype, ctx_, a, cfg_for(V, t, stream, 64, 1));

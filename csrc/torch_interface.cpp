@@ -515,6 +515,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.attr("ALGO_RING_SIMPLE") = (int)ALGO_RING_SIMPLE;
   m.attr("ALGO_ONESHOT") = (int)ALGO_ONESHOT;
   m.attr("ALGO_TWOSHOT") = (int)ALGO_TWOSHOT;
+  m.attr("ALGO_TWOSHOT_PIPELINED") = (int)ALGO_TWOSHOT_PIPELINED;
   m.attr("ALGO_DOUBLE_RING") = (int)ALGO_DOUBLE_RING;
   m.attr("ALGO_TREE") = (int)ALGO_TREE;
   m.attr("ALGO_NVLS") = (int)ALGO_NVLS;

@@ -33,6 +33,7 @@ ALGOS = {
     "ring_simple": ops.ALGO_RING_SIMPLE,
     "oneshot": ops.ALGO_ONESHOT,
     "twoshot": ops.ALGO_TWOSHOT,
+    "twoshot_pipelined": ops.ALGO_TWOSHOT_PIPELINED,   # three-stage pipeline; not yet timed on hardware
     "double_ring": ops.ALGO_DOUBLE_RING,
     "tree": ops.ALGO_TREE,
     "nvls": ops.ALGO_NVLS,

@@ -227,6 +227,25 @@ def test_all_to_all_pipelined(comms, world):
                     assert torch.equal(outs[r], want), (world, dtype, n, r)
 
 
+@pytest.mark.skipif(__import__("os").environ.get("PENNY_TEST_UNVERIFIED") != "1",
+                    reason="pipelined two-shot all-reduce: proven on the host simulator (incl. Thread/AddressSanitizer), "
+                           "not yet run on a GPU; set PENNY_TEST_UNVERIFIED=1")
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_all_reduce_twoshot_pipelined(comms, world):
+    comm = comms(world)
+    for dtype in (torch.float32, torch.bfloat16):
+        for n in (1, 1023, 4096, 65536, 3000000):
+            ins = make_inputs(world, n, dtype, seed=n)
+            want = torch.stack([x.float() for x in ins]).sum(0)
+            for _ in range(2):  # both scratch halves
+                outs = comm.all_reduce(ins, algo="twoshot_pipelined")
+                comm.check()
+                for r in range(world):
+                    torch.testing.assert_close(outs[r].float(), want, **TOL[dtype])
+                for r in range(1, world):
+                    assert torch.equal(outs[r], outs[0])
+
+
 def test_poisoned_scratch_never_reaches_a_result():
     """debug_poison: every check() overwrites all scratch regions with 0xFF bytes
     (NaN in every float format).  A protocol that consumed scratch it was not sent
