@@ -287,6 +287,15 @@ void Communicator::run_all_reduce_once(int algo, int dtype, const void* const* i
       bool in_heap = a[0].in_heap_off != kNotInHeap && t.symmetric_in;
       size_t out_off = heap_offset_of(out[0], 0);
       bool out_heap = out_off != kNotInHeap && t.symmetric_out;
+      // One-shot: every rank reads all inputs through the switch while the others
+      // may already be storing their results, so an output that overlaps the
+      // symmetric input would be overwritten before a peer has reduced it.  Such a
+      // call reads from a staged copy of the input instead.
+      if (oneshot && in_heap) {
+        const char* ib = (const char*)in[0];
+        const char* ob = (const char*)out[0];
+        if (ob < ib + n * es && ib < ob + n * es) in_heap = false;
+      }
       if (!in_heap) {
         ensure(stage_in_, bytes, "NVLS input staging");
         ckrt(cudaMemcpyAsync(local_ptr(stage_in_.off), in[0], n * es, cudaMemcpyDeviceToDevice,
@@ -552,11 +561,15 @@ void Communicator::all_gather_gemm(const void* a_shard, const void* b, void* out
                                    cudaStream_t stream) {
   if (emu_ && world_ != 1) throw std::runtime_error("penny: fused GEMMs need one process per GPU");
   const size_t need = sm100::ag_gemm_scratch_bytes(M, K);
-  if (ag_region_.bytes != need) {  // a new shape gets fresh memory: its halves must be exactly M x K
-    ag_region_.off = alloc(need);
-    ag_region_.bytes = need;
+  // A shape gets its own memory (its halves must be exactly M x K) the first time
+  // it is seen and the same memory ever after; the call order is the same on
+  // every rank, so the table is too.
+  Region& ag = ag_regions_[{M, K}];
+  if (ag.bytes != need) {
+    ag.off = alloc(need);
+    ag.bytes = need;
   }
-  ckrt(sm100::launch_ag_gemm(ctx_, ag_region_.off, ag_region_.bytes, a_shard, b, out, M, N, K, lda, ldb,
+  ckrt(sm100::launch_ag_gemm(ctx_, ag.off, ag.bytes, a_shard, b, out, M, N, K, lda, ldb,
                              ldc, side_ctas, error_word, stream),
        "all_gather_gemm (M must be a multiple of 128 * world, K and strides of 8)");
 }
@@ -593,7 +606,8 @@ void Communicator::host_barrier() {
 void Communicator::poison_scratch() {
   cudaDeviceSynchronize();
   host_barrier();  // nobody is still reading or writing a peer's scratch
-  const Region* regions[] = {&scratch_, &scratch_ll_, &scratch_pair_, &stage_in_, &stage_out_, &ag_region_};
+  std::vector<const Region*> regions = {&scratch_, &scratch_ll_, &scratch_pair_, &stage_in_, &stage_out_};
+  for (const auto& kv : ag_regions_) regions.push_back(&kv.second);
   for (const Region* r : regions) {
     if (r->bytes == 0) continue;
     for (int v = 0; v < views(); ++v) {

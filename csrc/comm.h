@@ -12,8 +12,10 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <map>
 #include <memory>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "algos.h"
@@ -141,7 +143,9 @@ class Communicator {
   Region scratch_ll_;    // halved, LL lines only
   Region scratch_pair_;  // exchange slot
   Region stage_in_, stage_out_;  // NVLS staging for tensors outside the heap
-  Region ag_region_;             // gathered A of all_gather_gemm, dedicated to one (M, K)
+  // gathered A of all_gather_gemm: one dedicated region per (M, K), kept for the
+  // communicator's lifetime and reused, so alternating shapes do not grow the heap
+  std::map<std::pair<int, int>, Region> ag_regions_;
   bool destroyed_ = false;
 };
 

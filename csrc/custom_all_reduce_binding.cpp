@@ -33,6 +33,14 @@ bool is_weak_contiguous(const at::Tensor& t) {
   return tail == t.numel() * (int64_t)t.element_size();
 }
 
+// The pull kernels move 16-byte vectors: a dense slice that starts off a 16-byte
+// boundary (buf[3:] of a bf16 tensor) must be refused on the host, where it is an
+// exception, not on the device, where it would be a misaligned-address fault.
+void check_aligned16(const at::Tensor& t, const char* what) {
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(t.data_ptr()) & 15u) == 0, "custom allreduce: ", what,
+              " must start on a 16-byte boundary (storage offset ", t.storage_offset(), ")");
+}
+
 CustomAllreduce* as_fa(fptr_t p) {
   TORCH_CHECK(p != 0, "custom allreduce: null handle");
   return reinterpret_cast<CustomAllreduce*>(p);
@@ -73,6 +81,8 @@ void bind_custom_all_reduce(py::module_& m) {
     TORCH_CHECK(inp.scalar_type() == out.scalar_type() && inp.numel() == out.numel(),
                 "custom allreduce: in/out mismatch");
     TORCH_CHECK(is_weak_contiguous(inp) && is_weak_contiguous(out), "custom allreduce: tensors must be dense");
+    check_aligned16(inp, "input");
+    check_aligned16(out, "output");
     const void* src = stage_input(inp, reg_buffer, reg_buffer_sz_bytes, stream);
     as_fa(fa)->allreduce(dtype_of(out), stream, src, out.data_ptr(), (size_t)out.numel());
   });
@@ -83,6 +93,8 @@ void bind_custom_all_reduce(py::module_& m) {
     cudaStream_t stream = at::cuda::getCurrentCUDAStream().stream();
     TORCH_CHECK(inp.scalar_type() == out.scalar_type(), "custom reduce_scatter: dtype mismatch");
     TORCH_CHECK(is_weak_contiguous(inp) && is_weak_contiguous(out), "custom reduce_scatter: tensors must be dense");
+    check_aligned16(inp, "input");
+    check_aligned16(out, "output");
     CustomAllreduce* f = as_fa(fa);
     // The output may be as large as the input (reference callers allocate it
     // with empty_like); the shard lands in its first numel / world elements.
@@ -97,6 +109,8 @@ void bind_custom_all_reduce(py::module_& m) {
     cudaStream_t stream = at::cuda::getCurrentCUDAStream().stream();
     TORCH_CHECK(inp.scalar_type() == out.scalar_type(), "custom all_gather: dtype mismatch");
     TORCH_CHECK(is_weak_contiguous(inp) && is_weak_contiguous(out), "custom all_gather: tensors must be dense");
+    check_aligned16(inp, "input");
+    check_aligned16(out, "output");
     CustomAllreduce* f = as_fa(fa);
     TORCH_CHECK(out.numel() >= inp.numel() * f->world(), "custom all_gather: output too small");
     const void* src = stage_input(inp, reg_buffer, reg_buffer_sz_bytes, stream);

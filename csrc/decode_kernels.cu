@@ -502,16 +502,21 @@ int noalloc_fail(int code, char* err, size_t err_len, const char* what, const ch
   return code;
 }
 
+// Raises the kernel's dynamic shared-memory limit on the current device.  Called
+// with g_noalloc_mu held (it guards the per-device "done" flags).
+cudaError_t noalloc_set_attr(int G) {
+  switch (G) {
+    case 1: return cudaFuncSetAttribute(penny::k_decode_attn<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, penny::kAttnSmem);
+    case 2: return cudaFuncSetAttribute(penny::k_decode_attn<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, penny::kAttnSmem);
+    case 4: return cudaFuncSetAttribute(penny::k_decode_attn<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, penny::kAttnSmem);
+    default: return cudaFuncSetAttribute(penny::k_decode_attn<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, penny::kAttnSmem);
+  }
+}
+
 template <int G>
 cudaError_t noalloc_launch(const void* qkv, const void* kcache, const void* vcache, const int* positions,
                            void* out, float* part_o, float* part_ml, int B, int Hq, int Hkv, int max_len,
-                           int splits, float scale, bool* attr_done, cudaStream_t stream) {
-  if (!*attr_done) {
-    cudaError_t rc = cudaFuncSetAttribute(penny::k_decode_attn<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          penny::kAttnSmem);
-    if (rc != cudaSuccess) return rc;
-    *attr_done = true;
-  }
+                           int splits, float scale, cudaStream_t stream) {
   dim3 grid(B, Hkv, splits);
   penny::k_decode_attn<G><<<grid, penny::kAttnWarps * 32, penny::kAttnSmem, stream>>>(
       (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, positions,
@@ -535,7 +540,10 @@ extern "C" __attribute__((visibility("default"))) int penny_decode_attention_noa
   const int G = Hq / Hkv;
   if (G != 1 && G != 2 && G != 4 && G != 8)
     return noalloc_fail(1, err, err_len, "penny_decode_attention_noalloc: Hq / Hkv must be 1, 2, 4 or 8", nullptr);
-  const size_t need = penny::decode_attn_workspace_bytes(B, Hq, splits);
+  // each factor is bounded on its own first, so that the product below cannot wrap
+  constexpr long long kMaxFactor = PENNY_NOALLOC_SCRATCH_BYTES / 520;
+  const bool factor_too_large = B > kMaxFactor || Hq > kMaxFactor;
+  const size_t need = factor_too_large ? ~(size_t)0 : penny::decode_attn_workspace_bytes(B, Hq, splits);
   if (need > (size_t)PENNY_NOALLOC_SCRATCH_BYTES) {
     char detail[160];
     snprintf(detail, sizeof(detail), "B * Hq * splits * 520 = %zu bytes needed, %u built in; lower `splits` or use "
@@ -547,7 +555,6 @@ extern "C" __attribute__((visibility("default"))) int penny_decode_attention_noa
   if (rc != cudaSuccess || dev < 0 || dev >= kMaxDevices)
     return noalloc_fail(3, err, err_len, "penny_decode_attention_noalloc: cudaGetDevice", cudaGetErrorString(rc));
   void* scratch = nullptr;
-  bool* attr_done = nullptr;
   {
     // once per device, with that device current: the device address of the array
     std::lock_guard<std::mutex> lk(g_noalloc_mu);
@@ -562,16 +569,25 @@ extern "C" __attribute__((visibility("default"))) int penny_decode_attention_noa
       g_noalloc_ptr[dev] = p;
     }
     scratch = g_noalloc_ptr[dev];
-    attr_done = &g_noalloc_attr[dev][G == 1 ? 0 : G == 2 ? 1 : G == 4 ? 2 : 3];
+    bool& attr_done = g_noalloc_attr[dev][G == 1 ? 0 : G == 2 ? 1 : G == 4 ? 2 : 3];
+    if (!attr_done) {
+      rc = noalloc_set_attr(G);
+      if (rc != cudaSuccess) {
+        (void)cudaGetLastError();
+        return noalloc_fail(3, err, err_len, "penny_decode_attention_noalloc: cudaFuncSetAttribute",
+                            cudaGetErrorString(rc));
+      }
+      attr_done = true;
+    }
   }
   float* part_o = reinterpret_cast<float*>(scratch);
   float* part_ml = part_o + (size_t)B * Hq * splits * penny::kD;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   switch (G) {
-    case 1: rc = noalloc_launch<1>(qkv, kcache, vcache, positions, out, part_o, part_ml, B, Hq, Hkv, max_len, splits, scale, attr_done, s); break;
-    case 2: rc = noalloc_launch<2>(qkv, kcache, vcache, positions, out, part_o, part_ml, B, Hq, Hkv, max_len, splits, scale, attr_done, s); break;
-    case 4: rc = noalloc_launch<4>(qkv, kcache, vcache, positions, out, part_o, part_ml, B, Hq, Hkv, max_len, splits, scale, attr_done, s); break;
-    default: rc = noalloc_launch<8>(qkv, kcache, vcache, positions, out, part_o, part_ml, B, Hq, Hkv, max_len, splits, scale, attr_done, s); break;
+    case 1: rc = noalloc_launch<1>(qkv, kcache, vcache, positions, out, part_o, part_ml, B, Hq, Hkv, max_len, splits, scale, s); break;
+    case 2: rc = noalloc_launch<2>(qkv, kcache, vcache, positions, out, part_o, part_ml, B, Hq, Hkv, max_len, splits, scale, s); break;
+    case 4: rc = noalloc_launch<4>(qkv, kcache, vcache, positions, out, part_o, part_ml, B, Hq, Hkv, max_len, splits, scale, s); break;
+    default: rc = noalloc_launch<8>(qkv, kcache, vcache, positions, out, part_o, part_ml, B, Hq, Hkv, max_len, splits, scale, s); break;
   }
   if (rc != cudaSuccess) {
     (void)cudaGetLastError();

@@ -6,7 +6,9 @@
 #include <pybind11/pybind11.h>
 #include <torch/extension.h>
 
+#include "gemm_decode_sm100.h"
 #include "gemm_skinny_sm100.h"
+#include "pdl.h"
 #include "gemm_sm100.h"
 
 namespace py = pybind11;
@@ -61,6 +63,38 @@ void bind_gemm(py::module_& m) {
         (int)out.stride(0), silu_pairs ? 1 : 0, penny_gemm_error_word(), at::cuda::getCurrentCUDAStream().stream());
     TORCH_CHECK(rc == cudaSuccess, "gemm_skinny: ", cudaGetErrorString(rc));
   }, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("silu_pairs") = false);
+  // Decode-batch linear: out[B, N] = x[B, K] @ w[N, K]^T for B <= 128.  One CTA per (weight tile, K
+  // range); the K ranges of a tile are reduced inside a thread-block cluster through distributed shared
+  // memory.  pdl: may start (and load w) while the previous kernel on the stream still runs, so w must not
+  // be written by that kernel.  silu_pairs: w's rows are blocks of 64 gate + 64 up rows and out is
+  // [B, N / 2] = silu(gate) * up.
+  m.def("gemm_decode", [](at::Tensor x, at::Tensor w, at::Tensor out, bool silu_pairs, int64_t splits, bool pdl,
+                          int64_t l2_budget, int64_t smem_kb) {
+    TORCH_CHECK(x.is_cuda() && w.is_cuda() && out.is_cuda(), "gemm_decode: CUDA tensors");
+    TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 &&
+                    out.scalar_type() == at::kBFloat16, "gemm_decode: bf16 only");
+    TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm_decode: 2-D tensors");
+    TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1, "gemm_decode: rows must be contiguous");
+    const int64_t B = x.size(0), K = x.size(1), N = w.size(0);
+    TORCH_CHECK(B >= 1 && B <= 128, "gemm_decode: 1 <= rows of x <= 128 (use gemm_bf16 beyond)");
+    TORCH_CHECK(w.size(1) == K && out.size(0) == B && out.size(1) == (silu_pairs ? N / 2 : N),
+                "gemm_decode: shape mismatch");
+    TORCH_CHECK(splits >= 0 && splits <= 8, "gemm_decode: 0 <= splits <= 8");
+    const at::cuda::OptionalCUDAGuard guard(x.device());
+    cudaError_t rc = penny::sm100::launch_gemm_decode(
+        x.data_ptr(), w.data_ptr(), out.data_ptr(), (int)B, (int)N, (int)K, (int)x.stride(0), (int)w.stride(0),
+        (int)out.stride(0), silu_pairs ? 1 : 0, (int)splits, pdl, (long long)l2_budget, (int)smem_kb,
+        penny_gemm_error_word(),
+        at::cuda::getCurrentCUDAStream().stream());
+    TORCH_CHECK(rc == cudaSuccess, "gemm_decode: ", cudaGetErrorString(rc));
+  }, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("silu_pairs") = false, py::arg("splits") = 0,
+     py::arg("pdl") = true, py::arg("l2_budget") = -1, py::arg("smem_kb") = 0);
+  m.def("gemm_decode_splits", [](int64_t B, int64_t N, int64_t K) {
+    return penny::sm100::gemm_decode_splits((int)B, (int)N, (int)K);
+  });
+  m.def("set_pdl", [](int64_t on) { penny::set_pdl_enabled((int)on); }, py::arg("on"),
+        "1 / 0: launch this library's decode kernels with / without programmatic dependent launch; -1: PENNY_PDL decides");
+  m.def("pdl_enabled", []() { return penny::pdl_enabled(); });
   m.def("gemm_set_split_tail", [](int64_t on) { penny::sm100::set_split_tail((int)on); }, py::arg("on"),
         "1 / 0: split (or not) the ragged last wave of the CTA-pair GEMM along K; -1: PENNY_GEMM_SPLIT_TAIL decides");
   // Synchronises; returns and clears the error code of the GEMM kernels (0 = fine).

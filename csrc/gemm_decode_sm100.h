@@ -1,0 +1,37 @@
+// Host API of the decode-batch linear (csrc/gemm_decode_sm100.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace penny {
+namespace sm100 {
+
+enum DecodeEpilogue : int {
+  DECODE_EPI_PLAIN = 0,
+  // W's rows come in blocks of 128 = 64 gate rows followed by the 64 up rows of
+  // the same features (N a multiple of 128); out is [B, N / 2] with
+  // out[b][blk * 64 + i] = silu(gate) * up.
+  DECODE_EPI_SILU_PAIRS = 1,
+};
+
+// out[B, N] = x[B, K] * W[N, K]^T, bf16, row-major with leading dimensions ldx /
+// ldw / ldo (elements); 1 <= B <= 128; K, ldx, ldw multiples of 8; x, w 16-byte aligned.
+//   splits          CTAs per weight tile (cluster size along K), 0 = choose
+//   pdl             launch with programmatic stream serialization: the kernel may
+//                   start, and load W, while the previous kernel on the stream is
+//                   still running.  W must then not be written by that kernel.
+//   l2_budget_bytes a whole W no larger than this is prefetched into L2 before the
+//                   dependency wait (-1 = default, 0 = only a rolling window)
+//   smem_kb         shared memory the TMA ring may grow to (0 = default: ~106 KB, so
+//                   that the next kernel of the step fits on the SM beside this one;
+//                   up to 226 for a kernel nothing needs to overlap with)
+// Allocates nothing; no workspace; safe to capture.  error_word as in launch_gemm_bf16.
+cudaError_t launch_gemm_decode(const void* x, const void* w, void* out, int B, int N, int K, int ldx, int ldw,
+                               int ldo, int epi, int splits, bool pdl, long long l2_budget_bytes,
+                               int smem_kb, uint32_t* error_word, cudaStream_t stream);
+
+// The cluster size launch_gemm_decode(splits = 0) uses for this shape on the current device.
+int gemm_decode_splits(int B, int N, int K);
+
+}  // namespace sm100
+}  // namespace penny

@@ -214,13 +214,19 @@ gemm_persistent_pair(const __grid_constant__ CUtensorMap map_a, const __grid_con
       __syncwarp();
     };
     PairWork w;
-    for (int it = 0; pair_work(s, num_kb, pair, npairs, it, w) && !*s_abort; ++it) {
+    // The four epilogue warps share named barriers (policy hooks, split tiles), so
+    // they must leave this loop at the same tile: after each bounded wait they
+    // vote, and a wait that ran out in ANY of them ends the loop for all.
+    bool aborted = false;
+    for (int it = 0; pair_work(s, num_kb, pair, npairs, it, w); ++it) {
       int m_blk, n_blk;
       decode(w.tile, m_blk, n_blk);
       const int ab = it & 1;
       const uint32_t ab_phase = (uint32_t)(it >> 1) & 1u;
-      if (!mbar_wait_abortable(&tmem_full[ab], ab_phase, s_abort)) {
-        if (lane == 0) fail(GEMM_ERR_EPILOGUE_WAIT);
+      const bool ok = !*s_abort && mbar_wait_abortable(&tmem_full[ab], ab_phase, s_abort);
+      if (!ok && lane == 0) fail(GEMM_ERR_EPILOGUE_WAIT);
+      if (!named_bar_all(3, 128, ok)) {
+        aborted = true;
         break;
       }
       tc_fence_after_sync();
@@ -310,7 +316,7 @@ gemm_persistent_pair(const __grid_constant__ CUtensorMap map_a, const __grid_con
       pol.tile_end(st, m_blk, n_blk);
       named_bar_sync(1, 128);  // s_last is rewritten by the next split tile only after all have read it
     }
-    pol.after_tiles(st, cta, ncta, (int)threadIdx.x - 64, error_word);
+    if (!aborted) pol.after_tiles(st, cta, ncta, (int)threadIdx.x - 64, error_word);
   } else {
     // ---------------------------------------------------------------- copy warps
     pol.side_work(st, cta, ncta, (int)threadIdx.x - 192, error_word);

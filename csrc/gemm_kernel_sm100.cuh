@@ -222,13 +222,19 @@ gemm_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;  // the TMEM lane quarter this warp may read
     int it = 0;
-    for (int tile = cta; tile < s.num_tiles && !*s_abort; tile += ncta, ++it) {
+    // The four epilogue warps share named barriers inside the policy hooks, so
+    // they must leave this loop at the same tile: after each bounded wait they
+    // vote, and a wait that ran out in ANY of them ends the loop for all.
+    bool aborted = false;
+    for (int tile = cta; tile < s.num_tiles; tile += ncta, ++it) {
       int m_blk, n_blk;
       decode(tile, m_blk, n_blk);
       const int ab = it & 1;
       const uint32_t ab_phase = (uint32_t)(it >> 1) & 1u;
-      if (!mbar_wait_abortable(&tmem_full[ab], ab_phase, s_abort)) {
-        if (lane == 0) fail(GEMM_ERR_EPILOGUE_WAIT);
+      const bool ok = !*s_abort && mbar_wait_abortable(&tmem_full[ab], ab_phase, s_abort);
+      if (!ok && lane == 0) fail(GEMM_ERR_EPILOGUE_WAIT);
+      if (!named_bar_all(3, 128, ok)) {
+        aborted = true;
         break;
       }
       tc_fence_after_sync();
@@ -273,7 +279,7 @@ gemm_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       if (lane == 0) mbar_arrive(&tmem_empty[ab]);
       pol.tile_end(st, m_blk, n_blk);
     }
-    pol.after_tiles(st, cta, ncta, (int)threadIdx.x - 64, error_word);
+    if (!aborted) pol.after_tiles(st, cta, ncta, (int)threadIdx.x - 64, error_word);
   }
   } else {
     // ---------------------------------------------------------------- copy warps

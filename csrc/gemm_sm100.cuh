@@ -259,5 +259,21 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// Named barrier with a vote: every one of the `nthreads` threads learns whether
+// ALL of them passed `ok`.  Used where warps that may have seen different
+// outcomes of a bounded wait must leave a loop at the same iteration.
+__device__ __forceinline__ bool named_bar_all(int id, int nthreads, bool ok) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 q, %3, 0;\n\t"
+      "bar.red.and.pred p, %1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"(id), "r"(nthreads), "r"((uint32_t)ok)
+      : "memory");
+  return r != 0;
+}
+
 }  // namespace sm100
 }  // namespace penny

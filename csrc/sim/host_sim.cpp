@@ -25,6 +25,7 @@
 #include "../algos.h"
 #include "../gemm_tile_order.h"
 #include "../skinny_order.h"
+#include "../decode_gemm_plan.h"
 #include "../all_reduce_oneshot.cuh"
 #include "../all_reduce_ring.cuh"
 #include "../all_reduce_tree.cuh"
@@ -345,6 +346,20 @@ int penny_skinny_segment(int tiles, int num_kb, int ctas, int cta, int i, int* o
 int penny_skinny_slot_of(int tiles, int num_kb, int ctas, int cta, int tile) {
   penny::sm100::SkinnyPlan p{tiles, num_kb, ctas};
   return penny::sm100::skinny_slot_of(p, cta, tile);
+}
+// Work split of the decode GEMM (decode_gemm_plan.h): out = {kb0, kb1, slice, recv_floats}
+// of CTA `r` of a cluster of `splits` working on a bt-wide batch tile.
+void penny_decode_plan(int num_kb, int splits, int r, int bt, long long* out) {
+  out[0] = penny::sm100::decode_kb_begin(num_kb, splits, r);
+  out[1] = penny::sm100::decode_kb_begin(num_kb, splits, r + 1);
+  out[2] = penny::sm100::decode_slice(bt, splits);
+  out[3] = (long long)penny::sm100::decode_recv_floats(bt, splits);
+}
+int penny_decode_recv_slot(int src, int dst) { return penny::sm100::decode_recv_slot(src, dst); }
+int penny_decode_choose_splits(int tiles, int num_kb, int sms, int gpc_sms) {
+  int cap[penny::sm100::kDecodeMaxSplits + 1];
+  penny::sm100::decode_model_capacity(sms, gpc_sms, cap);
+  return penny::sm100::decode_choose_splits(tiles, num_kb, cap);
 }
 // Tile -> (row block, column block) of the persistent GEMM kernels; pair_rank < 0
 // selects the single-CTA kernel, 0 / 1 the CTA of a pair.  Returns the number of

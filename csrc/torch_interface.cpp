@@ -330,18 +330,29 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                 "penny: weight must be [hidden] of the input dtype");
     std::vector<const void*> ip(nv), rp(nv);
     std::vector<void*> op(nv), rop(nv);
+    // every row is moved as 16-byte vectors: refuse a misaligned base here, on
+    // the host, rather than fault on the device
+    auto aligned16 = [](const at::Tensor& t, const char* what) {
+      TORCH_CHECK((reinterpret_cast<uintptr_t>(t.data_ptr()) & 15u) == 0, "penny: fused norm ", what,
+                  " must start on a 16-byte boundary");
+    };
+    aligned16(weight, "weight");
     for (int v = 0; v < nv; ++v) {
       check_dense(in[v], "input");
       check_dense(out[v], "output");
       TORCH_CHECK(out[v].numel() == in[v].numel(), "penny: output shape");
+      aligned16(in[v], "input");
+      aligned16(out[v], "output");
       ip[v] = in[v].data_ptr();
       op[v] = out[v].data_ptr();
       if (!residual.empty()) {
         check_dense(residual[v], "residual");
+        aligned16(residual[v], "residual");
         rp[v] = residual[v].data_ptr();
       }
       if (!residual_out.empty()) {
         check_dense(residual_out[v], "residual_out");
+        aligned16(residual_out[v], "residual_out");
         rop[v] = residual_out[v].data_ptr();
       }
     }

@@ -138,6 +138,10 @@ class CustomAllreduce:
             return False
         if not is_weak_contiguous(inp):
             return False
+        # the kernels move 16-byte vectors: a dense slice that starts off a 16-byte
+        # boundary (buf[3:] of a bf16 tensor) goes to the caller's fallback
+        if inp.data_ptr() % 16 != 0:
+            return False
         if self.world_size == 2 or self.fully_connected:
             return inp_size < self.max_size
         return False

@@ -128,3 +128,22 @@ def skinny_segments(tiles: int, num_kb: int, ctas: int, cta: int):
 
 def skinny_slot_of(tiles: int, num_kb: int, ctas: int, cta: int, tile: int) -> int:
     return sim_lib().penny_skinny_slot_of(tiles, num_kb, ctas, cta, tile)
+
+
+def decode_plan(num_kb: int, splits: int, r: int, bt: int = 64):
+    """K range and reduction layout of CTA `r` in a cluster of `splits` of the decode GEMM
+    (csrc/decode_gemm_plan.h): dict(kb0, kb1, slice, recv_floats)."""
+    lib = sim_lib()
+    out = (ctypes.c_longlong * 4)()
+    lib.penny_decode_plan(num_kb, splits, r, bt, out)
+    return dict(zip(("kb0", "kb1", "slice", "recv_floats"), [int(v) for v in out]))
+
+
+def decode_recv_slot(src: int, dst: int) -> int:
+    return sim_lib().penny_decode_recv_slot(src, dst)
+
+
+def decode_choose_splits(tiles: int, num_kb: int, sms: int = 148, gpc_sms: int = 18) -> int:
+    """Cluster size the decode GEMM picks for `tiles` weight tiles of 128 rows and `num_kb` K steps of
+    64 on a GPU of `sms` SMs in GPCs of `gpc_sms` (the launcher uses the occupancy API's figure)."""
+    return sim_lib().penny_decode_choose_splits(tiles, num_kb, sms, gpc_sms)

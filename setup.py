@@ -35,6 +35,7 @@ CUDA_SOURCES = [
     "csrc/gemm_sm100.cu",
     "csrc/gemm_fused_sm100.cu",
     "csrc/gemm_skinny_sm100.cu",
+    "csrc/gemm_decode_sm100.cu",
     "csrc/moe_dispatch_combine.cu",
 ]
 CPP_SOURCES = [

@@ -128,6 +128,12 @@ def test_custom_allreduce_dispatch_logic(monkeypatch):
     assert not car.should_custom_ar(torch.zeros(1 << 20, dtype=torch.bfloat16))    # 2 MiB >= max_size
     assert not car.should_custom_ar(torch.zeros(64, 64)[:, ::2])                   # not weakly contiguous
     assert car.should_custom_ar(torch.zeros(64, 64)[8:])                           # a dense tail of a storage is fine
+    # dense, 16-byte multiple, but starting 6 bytes into its storage: the kernels' 16-byte vectors would fault
+    odd = torch.zeros(4096 + 8, dtype=torch.bfloat16)[3:3 + 4096]
+    tail = torch.zeros(4096 + 3, dtype=torch.bfloat16)[3:]
+    assert tail.data_ptr() % 16 != 0 and not car.should_custom_ar(tail)
+    assert car.custom_all_reduce(tail) is None
+    del odd
 
     # eager: staged through this rank's registered buffer
     out = car.custom_all_reduce(ok)

@@ -217,3 +217,54 @@ def test_skinny_stream_k_split(tiles, num_kb, ctas):
         c = owner[(t, 0)]
         seg = [s for s in schedule.skinny_segments(tiles, num_kb, ctas, c) if s["tile"] == t][0]
         assert sharers == list(range(seg["c_lo"], seg["c_hi"] + 1))
+
+
+@pytest.mark.parametrize("num_kb,splits,bt", [(64, 8, 64), (64, 3, 64), (8, 4, 64), (28, 5, 64), (224, 7, 64),
+                                              (64, 6, 32), (7, 7, 128), (1, 1, 64), (13, 2, 128)])
+def test_decode_gemm_cluster_split(num_kb, splits, bt):
+    """Decode GEMM: the K ranges of a cluster cover every K step once and differ by at
+    most one step; the column slices of the batch tile cover it once and nobody owns nothing;
+    every source has its own slot in every receiver and the receive area is exactly
+    what the slots need."""
+    from penny_b200.parallel import schedule
+    chunk = bt
+    plans = [schedule.decode_plan(num_kb, splits, r, bt) for r in range(splits)]
+    assert plans[0]["kb0"] == 0 and plans[-1]["kb1"] == num_kb
+    sizes = []
+    for a, b in zip(plans, plans[1:]):
+        assert a["kb1"] == b["kb0"]
+    for p in plans:
+        assert p["kb1"] > p["kb0"]
+        sizes.append(p["kb1"] - p["kb0"])
+    assert max(sizes) - min(sizes) <= 1
+    sl = plans[0]["slice"]
+    owned = []
+    for r in range(splits):
+        lo, hi = r * sl, min(chunk, (r + 1) * sl)
+        assert hi > lo, "a CTA that owns no column would still be waited for"
+        owned += list(range(lo, hi))
+    assert owned == list(range(chunk))
+    for dst in range(splits):
+        slots = sorted(schedule.decode_recv_slot(src, dst) for src in range(splits) if src != dst)
+        assert slots == list(range(splits - 1))
+    want = 0 if splits == 1 else (splits - 1) * sl * 128
+    assert plans[0]["recv_floats"] == want
+
+
+def test_decode_gemm_split_choice_fills_the_gpu():
+    """Narrow tensor-parallel shards get enough K ranges to put CTAs on most SMs, all CTAs
+    stay resident at once, short K ranges are not split, wide matrices are left alone."""
+    from penny_b200.parallel import schedule
+    # (tiles, num_kb): TP-8 shards of a Llama-3-8B layer: qkv, o_proj, gate/up, down
+    assert schedule.decode_choose_splits(6, 64) == 8
+    assert schedule.decode_choose_splits(32, 8) == 1      # 8 K steps: a range of 4 is not worth a cluster
+    assert schedule.decode_choose_splits(28, 64) == 8
+    assert schedule.decode_choose_splits(32, 28) == 4     # ranges of 7 steps
+    for tiles, num_kb in [(6, 64), (28, 64), (32, 28), (48, 64), (32, 64), (32, 224), (126, 64), (24, 64), (112, 64)]:
+        s = schedule.decode_choose_splits(tiles, num_kb)
+        assert 1 <= s <= 8 and num_kb // s >= 6 and tiles * s <= 2 * 148
+    # whole-model matrices: gate/up (224 tiles) and the LM head (1002 tiles) need no split
+    assert schedule.decode_choose_splits(224, 64) == 1
+    assert schedule.decode_choose_splits(1002, 64) == 1
+    assert schedule.decode_choose_splits(32, 224) == 8
+    assert schedule.decode_choose_splits(126, 64) == 2

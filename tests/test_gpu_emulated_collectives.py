@@ -193,9 +193,6 @@ def test_bounded_wait_reports_status(comms):
     torch.testing.assert_close(outs[0], ins[0] + ins[1])
 
 
-@pytest.mark.skipif(__import__("os").environ.get("PENNY_TEST_UNVERIFIED") != "1",
-                    reason="pipelined reduce-scatter: proven on the host simulator (incl. Thread/AddressSanitizer), "
-                           "not yet run on a GPU; set PENNY_TEST_UNVERIFIED=1")
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_reduce_scatter_pipelined(comms, world):
     comm = comms(world)
@@ -210,9 +207,6 @@ def test_reduce_scatter_pipelined(comms, world):
                     torch.testing.assert_close(outs[r].float(), total[r * shard:(r + 1) * shard], **TOL[dtype])
 
 
-@pytest.mark.skipif(__import__("os").environ.get("PENNY_TEST_UNVERIFIED") != "1",
-                    reason="pipelined all-to-all: proven on the host simulator (incl. Thread/AddressSanitizer), "
-                           "not yet run on a GPU; set PENNY_TEST_UNVERIFIED=1")
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_all_to_all_pipelined(comms, world):
     comm = comms(world)
@@ -227,9 +221,6 @@ def test_all_to_all_pipelined(comms, world):
                     assert torch.equal(outs[r], want), (world, dtype, n, r)
 
 
-@pytest.mark.skipif(__import__("os").environ.get("PENNY_TEST_UNVERIFIED") != "1",
-                    reason="pipelined two-shot all-reduce: proven on the host simulator (incl. Thread/AddressSanitizer), "
-                           "not yet run on a GPU; set PENNY_TEST_UNVERIFIED=1")
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_all_reduce_twoshot_pipelined(comms, world):
     comm = comms(world)

@@ -96,6 +96,30 @@ def test_fused_gemm_kernels_single_rank():
         comm.close()
 
 
+def test_all_gather_gemm_alternating_shapes_reuse_their_regions():
+    """Each (M, K) keeps the gather region it was given on first use: alternating
+    two shapes many times must not grow the heap after the first pair."""
+    from penny_b200._ext import ops
+    from penny_b200.parallel.comm import Communicator
+    comm = Communicator.emulated(1, heap_bytes=128 << 20, timeout_ms=2000)
+    try:
+        shapes = [(256, 320), (384, 192)]
+        ws = {K: (torch.randn(128, K, device="cuda") * 0.5).bfloat16() for _, K in shapes}
+        free_after_first = None
+        for it in range(12):
+            for M, K in shapes:
+                a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+                out = comm.all_gather_gemm(a, ws[K])
+                assert ops.gemm_error() == 0
+                comm.check()
+                torch.testing.assert_close(out.float(), ref(a, ws[K]), atol=0.15, rtol=1.6e-2)
+            if free_after_first is None:
+                free_after_first = comm.heap_free()
+            assert comm.heap_free() == free_after_first
+    finally:
+        comm.close()
+
+
 def test_fused_gemm_kernels_single_rank_cta_pairs():
     """The same two fused kernels on shapes large enough (one 256 x 256 tile per
     CTA pair, K >= 1024) that their launchers choose the cta_group::2 kernel."""
@@ -156,3 +180,88 @@ def test_gemm_skinny_fused_silu_mul(shape):
     assert ops.gemm_error() == 0
     want = torch.nn.functional.silu(x.float() @ wg.float().t()) * (x.float() @ wu.float().t())
     torch.testing.assert_close(out.float(), want, atol=3e-2, rtol=2e-2)
+
+
+# ---------------------------------------------------------------------------------------------
+# decode GEMM: one CTA per (weight tile, K range), cluster reduction through distributed shared memory
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("splits", [0, 1, 2, 3, 5, 8])
+@pytest.mark.parametrize("shape", [(64, 768, 4096), (64, 4096, 512), (7, 1000, 264), (128, 4096, 1024),
+                                   (1, 128, 64), (33, 3584, 512), (64, 4096, 1792), (100, 1536, 2048),
+                                   (16, 2048, 4096), (8, 16032, 512)])
+def test_gemm_decode_matches_fp32(shape, splits):
+    """Every cluster size (and the automatic choice), every batch-tile width, ragged N
+    and B; called twice in a row with programmatic dependent launch on."""
+    from penny_b200._ext import ops
+    B, N, K = shape
+    if splits > K // 64 and K >= 64:
+        pytest.skip("more K ranges than K steps")
+    g = torch.Generator(device="cuda").manual_seed(B * 7 + N * 3 + K)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.5).bfloat16()
+    for rep in range(2):
+        x = (torch.randn(B, K, device="cuda", generator=g) * 0.5).bfloat16()
+        out = torch.full((B, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+        ops.gemm_decode(x, w, out, False, splits)
+        assert ops.gemm_error() == 0
+        torch.testing.assert_close(out.float(), ref(x, w), atol=2e-2 * (K ** 0.5) * 0.25 + 1e-2, rtol=1.6e-2)
+
+
+@pytest.mark.parametrize("splits", [0, 1, 4, 7])
+@pytest.mark.parametrize("shape", [(64, 3584, 4096), (5, 256, 320), (128, 1792, 1024), (20, 1792, 512)])
+def test_gemm_decode_fused_silu_mul(shape, splits):
+    """gate/up weight with rows interleaved in blocks of 64: the epilogue returns silu(gate) * up."""
+    from penny_b200._ext import ops
+    B, F, K = shape
+    if splits > K // 64:
+        pytest.skip("more K ranges than K steps")
+    g = torch.Generator(device="cuda").manual_seed(F + K)
+    wg = (torch.randn(F, K, device="cuda", generator=g) * 0.05).bfloat16()
+    wu = (torch.randn(F, K, device="cuda", generator=g) * 0.05).bfloat16()
+    w = torch.stack([wg.view(F // 64, 64, K), wu.view(F // 64, 64, K)], 1).reshape(2 * F, K).contiguous()
+    x = torch.randn(B, K, device="cuda", generator=g).bfloat16()
+    out = torch.full((B, F), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.gemm_decode(x, w, out, True, splits)
+    assert ops.gemm_error() == 0
+    want = torch.nn.functional.silu(x.float() @ wg.float().t()) * (x.float() @ wu.float().t())
+    torch.testing.assert_close(out.float(), want, atol=3e-2, rtol=2e-2)
+
+
+def test_gemm_decode_chain_in_a_cuda_graph_with_and_without_pdl():
+    """A chain of dependent decode GEMMs (each reads the previous one's output) captured in a
+    CUDA graph: with programmatic dependent launch the kernels overlap their prologues but
+    must still see their predecessor's result; the answer equals the serialised run."""
+    from penny_b200._ext import ops
+    g = torch.Generator(device="cuda").manual_seed(5)
+    B, H = 64, 1024
+    ws = [(torch.randn(H, H, device="cuda", generator=g) * (1.0 / H ** 0.5)).bfloat16() for _ in range(6)]
+    x0 = torch.randn(B, H, device="cuda", generator=g).bfloat16()
+    bufs = [torch.empty(B, H, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+
+    def chain(pdl):
+        cur = x0
+        for i, w in enumerate(ws):
+            ops.gemm_decode(cur, w, bufs[i & 1], False, 0, pdl)
+            cur = bufs[i & 1]
+        return cur
+
+    want = x0.float()
+    for w in ws:
+        want = (want @ w.float().t()).bfloat16().float()
+    results = {}
+    for pdl in (False, True):
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            chain(pdl)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = chain(pdl)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        assert ops.gemm_error() == 0
+        results[pdl] = out.float().clone()
+        torch.testing.assert_close(results[pdl], want, atol=6e-2, rtol=5e-2)
+    assert torch.equal(results[False], results[True])
