@@ -33,6 +33,7 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 PUBLISHED_TOKS = None  # the reference publishes no tokens/s figure for this config
+MODEL_NAME = "Llama-3-8B-shaped (hidden 4096, 32 layers, 32q/8kv heads, FFN 14336, vocab 128256)"
 
 
 def parse():
@@ -44,7 +45,9 @@ def parse():
     p.add_argument("--batch", type=int, default=64)
     p.add_argument("--kv-len", type=int, default=2048)
     p.add_argument("--backend", default="penny", choices=["penny", "penny_unfused", "nccl"])
-    p.add_argument("--proto", default="auto", choices=["auto", "ll", "flag", "nvls"])
+    p.add_argument("--proto", default="auto", choices=["auto", "ll", "flag", "nvls", "nvls_oneshot"])
+    p.add_argument("--linears", default="penny", choices=["penny", "cublas"],
+                   help="penny: this library's tcgen05 decode GEMM (default); cublas: torch.matmul, for comparison")
     p.add_argument("--layers", type=int, default=32, help="debug only: anything but 32 is not the named config")
     p.add_argument("--no-graph", action="store_true")
     return p.parse_args()
@@ -185,7 +188,11 @@ def run_penny(args):
     cfg.layers = args.layers
     max_len = args.kv_len + args.steps * 2 + args.warmup * 2 + 64
     model = LlamaTPDecoder(cfg, comm=comm, rank=rank, world=world, max_batch=args.batch, max_len=max_len,
-                           backend=args.backend, proto=args.proto, use_graph=not args.no_graph)
+                           backend=args.backend, proto=args.proto, use_graph=not args.no_graph, linears=args.linears)
+
+    def ops_pdl_enabled():
+        from penny_b200._ext import ops
+        return ops.pdl_enabled()
     model.fill_synthetic_kv(args.kv_len)
     model.capture()
 
@@ -241,13 +248,16 @@ def run_penny(args):
             "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic tokens + synthetic KV cache, random-init weights",
             "impl": "penny_b200",
-            "config": {"model": "Llama-3-8B-shaped (hidden 4096, 32 layers, 32q/8kv heads, FFN 14336, vocab 128256)"
-                       if args.layers == 32 else f"DEBUG {args.layers} layers",
+            "config": {"model": MODEL_NAME if args.layers == 32 else f"DEBUG {args.layers} layers",
                        "global_batch": args.batch, "seq_len": args.kv_len, "parallelism": f"tp{world}",
-                       "backend": args.backend, "proto": model.proto, "cuda_graph": not args.no_graph,
-                       "l2": "inputs larger than L2: every step streams %.2f GB of weights and KV per GPU"
-                             % ((model.weight_bytes() - model.embed.numel() * 2
-                                 + 2 * args.batch * model.Hkv * args.kv_len * 128 * 2 * cfg.layers) / 1e9)},
+                       "cuda_graph": not args.no_graph,
+                       "l2": "inputs larger than L2 (weights + KV streamed every step)"},
+            "impl_detail": {"backend": args.backend, "proto": model.proto, "linears": args.linears,
+                            "programmatic_dependent_launch": bool(ops_pdl_enabled()),
+                            "streamed_gb_per_gpu_per_step": round(
+                                (model.weight_bytes() - model.embed.numel() * 2
+                                 + 2 * args.batch * model.Hkv * args.kv_len * 128 * 2 * cfg.layers) / 1e9, 2),
+                            "attended_kv_len": args.kv_len + 1},
             "clocks": clocks,
             "e2e": {"value": round(e2e_toks, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / args.steps, 4),
                     "h2d_bytes_per_step": args.batch * 8, "d2h_bytes_per_step": args.batch * 8},
@@ -300,7 +310,7 @@ def run_reference(args):
     ones = torch.ones(H, dtype=dt, device=dev)
     layers = [dict(wqkv=rnd((Hq + 2 * Hkv) * D, H), wo=rnd(H, Hq * D), wgu=rnd(2 * Fl, H), wdown=rnd(H, Fl))
               for _ in range(L)]
-    max_len = args.kv_len + 2 * (args.steps + args.warmup) + 8
+    max_len = args.kv_len + args.steps + args.warmup + 2  # every phase restarts at kv_len
     kc = [torch.randn(B, Hkv, max_len, D, device=dev, generator=g, dtype=torch.float32).to(dt) for _ in range(L)]
     vc = [torch.randn(B, Hkv, max_len, D, device=dev, generator=g, dtype=torch.float32).to(dt) for _ in range(L)]
     tokens = torch.randint(0, 128256, (B,), device=dev, generator=g)
@@ -313,13 +323,17 @@ def run_reference(args):
     mask = torch.full((1, 1, 1, max_len), float("-inf"), dtype=dt, device=dev)
     mask[..., :args.kv_len] = 0
 
+    served = {"reference_kernel": 0, "nccl_fallback": 0}  # all-reduce calls of the step being traced
+
     def all_reduce(x):
         if world == 1:
             return x
         out = car.custom_all_reduce(x)
         if out is None:
+            served["nccl_fallback"] += 1
             dist.all_reduce(x)
             return x
+        served["reference_kernel"] += 1
         return out
 
     def rope(t, cos, sin):
@@ -375,6 +389,7 @@ def run_reference(args):
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
+        served.update(reference_kernel=0, nccl_fallback=0)
         if car is not None:
             with car.capture():
                 with torch.cuda.graph(graph):
@@ -436,11 +451,15 @@ def run_reference(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic tokens + synthetic KV cache, random-init weights", "impl": "reference",
-            "config": {"model": "Llama-3-8B-shaped (hidden 4096, 32 layers, 32q/8kv heads, FFN 14336, vocab 128256)"
-                       if L == 32 else f"DEBUG {L} layers", "global_batch": B, "seq_len": args.kv_len,
-                       "parallelism": f"tp{world}", "allreduce": "reference CustomAllreduce, NCCL fallback", "mode": mode,
-                       "model_code": "plain PyTorch (the reference ships no model)",
+            "config": {"model": MODEL_NAME if L == 32 else f"DEBUG {L} layers", "global_batch": B,
+                       "seq_len": args.kv_len, "parallelism": f"tp{world}", "cuda_graph": graph is not None,
                        "l2": "inputs larger than L2 (weights + KV streamed every step)"},
+            "impl_detail": {"allreduce": "reference CustomAllreduce (custom_all_reduce under its capture()), "
+                                         "torch.distributed NCCL when it returns None",
+                            "allreduce_calls_per_step": dict(served), "mode": mode,
+                            "model_code": "plain PyTorch (the reference ships no model)",
+                            "attended_kv_len": f"{max_len} cache rows under an additive mask "
+                                               f"({args.kv_len + 1} of them unmasked in the first timed step)"},
             "clocks": clocks,
             "e2e": {"value": round(B * args.steps / (e2e_ms * 1e-3), 1), "unit": "tokens/s",
                     "ms_per_step": round(e2e_ms / args.steps, 4), "h2d_bytes_per_step": B * 8,

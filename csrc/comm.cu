@@ -117,6 +117,7 @@ LaunchCfg Communicator::cfg_for(size_t vecs, const Tuning& t, cudaStream_t s, in
   cfg.threads = t.threads > 0 ? t.threads : 512;
   cfg.stream = s;
   cfg.emu_world = emu_ ? world_ : 0;
+  cfg.pdl = true;  // the kernel shell waits for its predecessor before it touches anything
   // emulation: all virtual ranks' blocks must be co-resident (one 512-thread
   // block per SM in the worst case)
   if (emu_) max_blocks = std::max(1, std::min(max_blocks, 128 / world_));
@@ -508,8 +509,14 @@ void Communicator::fused_ar_rmsnorm(int dtype, int proto, const void* const* in,
   cfg.threads = threads;
   cfg.stream = stream;
   cfg.emu_world = emu_ ? world_ : 0;
+  cfg.pdl = true;  // sits between the GEMMs of a decode step: overlap its launch with the producer's tail
   int max_blocks = emu_ ? std::max(1, 128 / world_) : 256;
-  if (proto == FUSED_PROTO_NVLS) {
+  if (proto == FUSED_PROTO_NVLS_ONESHOT) {
+    if (!has_multicast()) throw std::runtime_error("penny: NVLS fused norm without multicast");
+    if (a[0].in_heap_off == kNotInHeap || !t.symmetric_in)
+      throw std::runtime_error("penny: one-shot NVLS fused norm needs a symmetric heap tensor for in");
+    cfg.blocks = t.blocks > 0 ? t.blocks : std::min(max_blocks, std::max(1, rows));
+  } else if (proto == FUSED_PROTO_NVLS) {
     if (!has_multicast()) throw std::runtime_error("penny: NVLS fused norm without multicast");
     if (a[0].in_heap_off == kNotInHeap || a[0].out_heap_off == kNotInHeap || !t.symmetric_in ||
         !t.symmetric_out)

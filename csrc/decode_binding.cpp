@@ -59,6 +59,30 @@ void bind_decode(py::module_& m) {
                                (int)kcache.size(2), (int)splits, (float)scale, cur()),
        "decode_attention");
   });
+  m.def("decode_attn_fused_workspace_bytes", [](int64_t B, int64_t Hq, int64_t Hkv, int64_t splits) {
+    return (int64_t)decode_attn_fused_workspace_bytes((int)B, (int)Hq, (int)Hkv, (int)splits);
+  });
+  // rope + KV append + split-KV attention + merge in one launch; qkv is the raw projection of the new token
+  m.def("decode_attention_fused", [](at::Tensor qkv, at::Tensor kcache, at::Tensor vcache, at::Tensor positions,
+                                     at::Tensor out, at::Tensor workspace, int64_t Hq, int64_t Hkv, int64_t splits,
+                                     double scale, double theta, bool pdl) {
+    need(bf16_cuda(qkv) && bf16_cuda(kcache) && bf16_cuda(vcache) && bf16_cuda(out), "decode_attention_fused expects contiguous bf16 CUDA tensors");
+    need(positions.is_cuda() && positions.scalar_type() == at::kInt && positions.is_contiguous(), "positions must be int32 CUDA");
+    need(kcache.dim() == 4 && vcache.sizes() == kcache.sizes(), "caches must be [B, Hkv, max_len, D]");
+    const int64_t B = qkv.size(0), D = kcache.size(3);
+    need(qkv.dim() == 2 && qkv.size(1) == (Hq + 2 * Hkv) * D && out.numel() == B * Hq * D && kcache.size(0) == B &&
+             kcache.size(1) == Hkv && positions.numel() == B, "decode_attention_fused shapes");
+    need(workspace.is_cuda() && (int64_t)workspace.nbytes() >=
+                                    (int64_t)decode_attn_fused_workspace_bytes((int)B, (int)Hq, (int)Hkv, (int)splits),
+         "workspace too small (decode_attn_fused_workspace_bytes)");
+    need(((uintptr_t)workspace.data_ptr() & 15) == 0, "workspace must be 16-byte aligned");
+    const at::cuda::OptionalCUDAGuard guard(qkv.device());
+    ck(launch_decode_attention_fused(qkv.data_ptr(), kcache.data_ptr(), vcache.data_ptr(), positions.data_ptr<int>(),
+                                     out.data_ptr(), workspace.data_ptr(), (int)B, (int)Hq, (int)Hkv, (int)D,
+                                     (int)kcache.size(2), (int)splits, (float)scale, (float)theta, pdl, cur()),
+       "decode_attention_fused");
+  }, py::arg("qkv"), py::arg("kcache"), py::arg("vcache"), py::arg("positions"), py::arg("out"), py::arg("workspace"),
+     py::arg("Hq"), py::arg("Hkv"), py::arg("splits"), py::arg("scale"), py::arg("theta"), py::arg("pdl") = true);
   m.def("silu_mul", [](at::Tensor gate_up, at::Tensor out) {
     need(bf16_cuda(gate_up) && bf16_cuda(out) && gate_up.dim() == 2, "silu_mul expects [rows, 2F] bf16");
     const int64_t rows = gate_up.size(0), F = gate_up.size(1) / 2;

@@ -26,6 +26,16 @@ cudaError_t launch_decode_attention(const void* qkv, const void* kcache, const v
                                     int Hkv, int D, int max_len, int splits, float scale,
                                     cudaStream_t stream);
 
+// One launch for rope + KV append + split-KV attention + merge (csrc/decode_attention_fused.cu).
+// qkv holds the UNROTATED projections of the new token; rows [0, positions[b]) of the caches are
+// attended to together with the new token, whose rotated k and v are stored at row positions[b].
+// workspace: decode_attn_fused_workspace_bytes, zeroed once before the first call (its tail holds
+// self-resetting arrival counters).  pdl: launch with programmatic stream serialization.
+size_t decode_attn_fused_workspace_bytes(int B, int Hq, int Hkv, int splits);
+cudaError_t launch_decode_attention_fused(const void* qkv, void* kcache, void* vcache, const int* positions,
+                                          void* out, void* workspace, int B, int Hq, int Hkv, int D, int max_len,
+                                          int splits, float scale, float theta, bool pdl, cudaStream_t stream);
+
 // gate_up: [rows, 2F] (gate | up) -> out [rows, F] = silu(gate) * up
 cudaError_t launch_silu_mul(const void* gate_up, void* out, int rows, int F, cudaStream_t stream);
 

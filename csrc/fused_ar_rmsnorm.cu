@@ -8,7 +8,7 @@
 // that re-reads it.  Here the rows never leave registers between the reduction
 // and the normalisation, and there is one launch instead of two or three.
 //
-// Three transports, all one block per row:
+// Transports, all one block per row:
 //   LL    every rank pushes its partial rows to every peer as flag-in-data
 //         lines and polls for the peers' lines: no barrier, lowest latency, 2x
 //         wire bytes.  Best for a handful of rows.
@@ -17,6 +17,8 @@
 //         row (multimem.ld_reduce), normalises it and multicasts the result
 //         (multimem.st).  The residual stream stays sharded: each rank only
 //         keeps the residual of the rows it owns.  Least wire traffic.
+//   NVLS one-shot  every rank pulls all rows switch-reduced and normalises them
+//         itself: half the latency steps, `world` times the wire bytes.
 // Plus the communication-free kernel (add_rmsnorm) used at world size 1.
 //
 // The reference stops at the plain all-reduce (penny/custom_all_reduce.py:229-267);
@@ -25,6 +27,7 @@
 #include "all_reduce_oneshot.cuh"
 #include "fused_ops.h"
 #include "launch.cuh"
+#include "pdl.h"
 #include "schedule.h"
 
 namespace penny {
@@ -85,7 +88,9 @@ template <typename T>
 __global__ void __launch_bounds__(512) k_add_rmsnorm(const FusedNormArgs a) {
   constexpr int E = 16 / sizeof(T);
   __shared__ float smem[32];
+  pdl_launch_dependents();
   const int HV = a.hidden / E;
+  pdl_wait();
   for (size_t row = blockIdx.x; row < (size_t)a.rows; row += gridDim.x) {
     float z[kMaxVecPerThread][E];
     int nv = 0;
@@ -235,59 +240,99 @@ __device__ __forceinline__ void mm_st(void* p, const V16& v) {
                : "memory");
 }
 
-template <typename T>
-struct FusedNvlsNorm {
-  static __device__ void body(const CommCtx& c, int rank, const FusedNormArgs& a, const Blk& b,
-                              u64 seq, int& s_abort) {
-    constexpr int E = 16 / sizeof(T);
-    __shared__ float smem[32];
-    const int HV = a.hidden / E;
-    const Span mine = split_span((size_t)a.rows, c.world, rank);
-    const T* w = reinterpret_cast<const T*>(a.weight);
-    PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 1), s_abort);
-    if (s_abort) return;
+// Two transports through the switch:
+//   two-shot  rows are sharded over the ranks; the owner pulls the switch-reduced
+//             row, normalises it and multicasts the result (multimem.st) into every
+//             rank's `out`; a second flag exchange tells the peers that the rows
+//             have landed.  The residual stream stays sharded (a rank keeps the
+//             residual of the rows it owns).  Least wire traffic.
+//   one-shot  every rank pulls ALL rows switch-reduced and normalises them itself:
+//             one flag exchange and one round trip instead of two of each, `world`
+//             times the wire bytes, no multicast store, `out` is ordinary local
+//             memory and the residual stream is replicated.  There is no trailing
+//             barrier: a peer may still be reading this rank's `in` when the call
+//             returns, so CONSECUTIVE CALLS MUST ALTERNATE BETWEEN TWO INPUT
+//             BUFFERS (a rank can be at most one call ahead of any other: it cannot
+//             pass the opening barrier of call k + 1 before every rank has finished
+//             call k).  For a handful of rows (decode batches up to ~32).
+// Launched with programmatic stream serialization: the norm weight (a constant)
+// is fetched and the block is resident before the producing GEMM has finished.
+template <typename T, bool ONESHOT>
+__global__ void __launch_bounds__(512) k_fused_nvls_norm(const CommCtx c, const FusedNormArgs a) {
+  constexpr int E = 16 / sizeof(T);
+  __shared__ float smem[32];
+  __shared__ int s_abort;
+  pdl_launch_dependents();
+  const int rank = c.rank;
+  const Blk b{(int)blockIdx.x, (int)gridDim.x, (int)blockDim.x};
+  const int HV = a.hidden / E;
+  const T* w = reinterpret_cast<const T*>(a.weight);
+  V16 wv[kMaxVecPerThread];
+#pragma unroll
+  for (int k = 0; k < kMaxVecPerThread; ++k) {
+    const int v = threadIdx.x + k * blockDim.x;
+    if (v < HV) wv[k] = ld16(w + (size_t)v * E);
+  }
+  if (threadIdx.x == 0) s_abort = 0;
+  pdl_wait();  // the partial sums of this rank are complete; the call counter is final
+  const u64 seq = begin_call(c, rank, SEQ_ALL);
+  PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 1), s_abort);
+  if (!s_abort) {
+    Span mine = split_span((size_t)a.rows, c.world, rank);
+    if (ONESHOT) {
+      mine.begin = 0;
+      mine.end = (size_t)a.rows;
+    }
     for (size_t row = mine.begin + b.bid; row < mine.end; row += b.nblocks) {
       float z[kMaxVecPerThread][E];
+      V16 red[kMaxVecPerThread], res[kMaxVecPerThread];
       int nv = 0;
-      float ss = 0.f;
+      // every load of the row is in flight before the first one is used
 #pragma unroll
       for (int k = 0; k < kMaxVecPerThread; ++k) {
         const int v = threadIdx.x + k * blockDim.x;
         if (v < HV) {
           nv = k + 1;
           const size_t eoff = (row * a.hidden + (size_t)v * E) * sizeof(T);
-          unpack_set<T>(mm_ld_reduce<T>(c.mc + a.in_heap_off + eoff), z[k]);
-          if (a.residual)
-            unpack_add<T>(
-                ld16(reinterpret_cast<const T*>(a.residual) + row * a.hidden + (size_t)v * E), z[k]);
+          red[k] = mm_ld_reduce<T>(c.mc + a.in_heap_off + eoff);
+          if (a.residual) res[k] = ld16(reinterpret_cast<const T*>(a.residual) + row * a.hidden + (size_t)v * E);
+        }
+      }
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < kMaxVecPerThread; ++k) {
+        if (k < nv) {
+          unpack_set<T>(red[k], z[k]);
+          if (a.residual) unpack_add<T>(res[k], z[k]);
 #pragma unroll
           for (int i = 0; i < E; ++i) ss += z[k][i] * z[k][i];
         }
       }
       ss = block_sum(ss, smem);
       const float rstd = rsqrtf(ss / (float)a.hidden + a.eps);
-      T* rout =
-          a.residual_out ? reinterpret_cast<T*>(a.residual_out) + row * (size_t)a.hidden : nullptr;
+      T* rout = a.residual_out ? reinterpret_cast<T*>(a.residual_out) + row * (size_t)a.hidden : nullptr;
 #pragma unroll
       for (int k = 0; k < kMaxVecPerThread; ++k) {
         if (k < nv) {
           const int v = threadIdx.x + k * blockDim.x;
           if (rout) st16(rout + (size_t)v * E, pack<T>(z[k]));
-          float wv[E], o[E];
-          unpack_set<T>(ld16(w + (size_t)v * E), wv);
+          float wf[E], o[E];
+          unpack_set<T>(wv[k], wf);
 #pragma unroll
-          for (int i = 0; i < E; ++i) o[i] = z[k][i] * rstd * wv[i];
-          const size_t eoff = (row * a.hidden + (size_t)v * E) * sizeof(T);
-          mm_st(c.mc + a.out_heap_off + eoff, pack<T>(o));
+          for (int i = 0; i < E; ++i) o[i] = z[k][i] * rstd * wf[i];
+          if (ONESHOT) {
+            st16(reinterpret_cast<T*>(a.out) + row * (size_t)a.hidden + (size_t)v * E, pack<T>(o));
+          } else {
+            const size_t eoff = (row * a.hidden + (size_t)v * E) * sizeof(T);
+            mm_st(c.mc + a.out_heap_off + eoff, pack<T>(o));
+          }
         }
       }
     }
-    PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 2), s_abort);
+    if (!ONESHOT) PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 2), s_abort);
   }
-  static __device__ void run(const CommCtx& c, int rank, const FusedNormArgs& a, const Blk& b) {
-    run_collective<FusedNvlsNorm<T>, FusedNormArgs>(c, rank, a, b);
-  }
-};
+  end_call(c, rank, b, seq, SEQ_ALL);
+}
 
 static bool shape_ok(int dtype, const FusedNormArgs& a, int threads) {
   const int E = 16 / dtype_size(dtype);
@@ -298,19 +343,28 @@ static bool shape_ok(int dtype, const FusedNormArgs& a, int threads) {
 cudaError_t launch_add_rmsnorm(int dtype, const FusedNormArgs& a, int blocks, int threads,
                                cudaStream_t stream) {
   if (!shape_ok(dtype, a, threads)) return cudaErrorInvalidValue;
-  PENNY_DISPATCH_DTYPE(dtype, T, (k_add_rmsnorm<T><<<blocks, threads, 0, stream>>>(a)));
-  return cudaGetLastError();
+  cudaError_t rc = cudaErrorInvalidValue;
+  PENNY_DISPATCH_DTYPE(dtype, T, rc = launch_kernel_ex(k_add_rmsnorm<T>, dim3(blocks), dim3(threads), 0, stream, true, 1, a));
+  return rc;
 }
 
 cudaError_t launch_fused_ar_rmsnorm(int dtype, int proto, const CommCtx& c, const FusedNormArgs* a,
                                     const LaunchCfg& cfg) {
   if (!shape_ok(dtype, a[0], cfg.threads)) return cudaErrorInvalidValue;
   cudaError_t rc = cudaErrorInvalidValue;
-  if (proto == FUSED_PROTO_NVLS) {
+  if (proto == FUSED_PROTO_NVLS || proto == FUSED_PROTO_NVLS_ONESHOT) {
+    const bool oneshot = proto == FUSED_PROTO_NVLS_ONESHOT;
     if (c.mc == nullptr || cfg.emu_world > 0 || a[0].in_heap_off == kNotInHeap ||
-        a[0].out_heap_off == kNotInHeap)
+        (!oneshot && a[0].out_heap_off == kNotInHeap))
       return cudaErrorNotSupported;
-    PENNY_DISPATCH_DTYPE(dtype, T, rc = (launch_body<FusedNvlsNorm<T>, FusedNormArgs>(c, a, cfg)));
+    if (cfg.blocks < 1 || cfg.blocks > kMaxBlocks || cfg.threads < 32 || cfg.threads > 512)
+      return cudaErrorInvalidConfiguration;
+    PENNY_DISPATCH_DTYPE(dtype, T, {
+      rc = oneshot ? launch_kernel_ex(k_fused_nvls_norm<T, true>, dim3(cfg.blocks), dim3(cfg.threads), 0, cfg.stream,
+                                      true, 1, c, a[0])
+                   : launch_kernel_ex(k_fused_nvls_norm<T, false>, dim3(cfg.blocks), dim3(cfg.threads), 0, cfg.stream,
+                                      true, 1, c, a[0]);
+    });
     return rc;
   }
   PENNY_DISPATCH_DTYPE(dtype, T, PENNY_DISPATCH_WORLD(c.world, NG, return cudaErrorInvalidValue, {

@@ -8,7 +8,7 @@ namespace penny {
 
 struct LaunchCfg;
 
-enum FusedProto : int { FUSED_PROTO_LL = 0, FUSED_PROTO_FLAG = 1, FUSED_PROTO_NVLS = 2 };
+enum FusedProto : int { FUSED_PROTO_LL = 0, FUSED_PROTO_FLAG = 1, FUSED_PROTO_NVLS = 2, FUSED_PROTO_NVLS_ONESHOT = 3 };
 
 // all-reduce + residual add + RMSNorm over [rows, hidden]
 struct FusedNormArgs {

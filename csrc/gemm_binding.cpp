@@ -92,6 +92,15 @@ void bind_gemm(py::module_& m) {
   m.def("gemm_decode_splits", [](int64_t B, int64_t N, int64_t K) {
     return penny::sm100::gemm_decode_splits((int)B, (int)N, (int)K);
   });
+  m.def("gemm_decode_capacity", [](int64_t B, int64_t splits) {
+    return penny::sm100::gemm_decode_capacity((int)B, (int)splits);
+  });
+  m.def("gemm_decode_stamps", [](int64_t max_ctas) {
+    auto t = torch::zeros({max_ctas, 8}, torch::TensorOptions().dtype(torch::kInt64));
+    cudaDeviceSynchronize();
+    const int n = penny::sm100::gemm_decode_stamps(reinterpret_cast<unsigned long long*>(t.data_ptr<int64_t>()), (int)max_ctas);
+    return t.narrow(0, 0, n);
+  }, py::arg("max_ctas") = 512, "timestamps of the last gemm_decode launch (needs PENNY_DEC_STAMPS=1)");
   m.def("set_pdl", [](int64_t on) { penny::set_pdl_enabled((int)on); }, py::arg("on"),
         "1 / 0: launch this library's decode kernels with / without programmatic dependent launch; -1: PENNY_PDL decides");
   m.def("pdl_enabled", []() { return penny::pdl_enabled(); });

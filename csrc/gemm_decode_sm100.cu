@@ -74,6 +74,11 @@ namespace {
 constexpr int kDecThreads = 192;
 constexpr int kMaxStages = 8;
 
+// Diagnostics: with PENNY_DEC_STAMPS=1 the first 512 CTAs of a launch record
+// %globaltimer at eight points (see gemm_decode_stamps in the header).
+constexpr int kStampCtas = 512, kStampPoints = 8;
+__device__ unsigned long long g_dec_stamps[kStampCtas * kStampPoints];
+
 struct DecodeArgs {
   __nv_bfloat16* out;
   int ldo;
@@ -84,6 +89,7 @@ struct DecodeArgs {
   int l2_prefetch;  // K steps beyond the ring that the producer prefetches into L2 before the dependency wait
   int l2_ahead;     // steady state: W of step i + l2_ahead is prefetched into L2 when step i is loaded
   int k_stagger;    // 1: tiles start their K range at different offsets
+  int stamps;       // 1: record timestamps
   int epi;          // DECODE_EPI_*
 };
 
@@ -107,7 +113,6 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, const float
                "f"(v.w)
                : "memory");
 }
-__device__ __forceinline__ void fence_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -152,11 +157,16 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   uint64_t* full = bars;
   uint64_t* empty = bars + kMaxStages;
   uint64_t* tmem_full = bars + 2 * kMaxStages;
-  uint64_t* recv_bar = bars + 2 * kMaxStages + 1;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 2);
+  uint64_t* recv_bar = bars + 2 * kMaxStages + 1;  // [4]: one per epilogue warp (row quarter)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 5);
   volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   pdl_launch_dependents();
+  const int cta_lin = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+  auto stamp = [&](int point) {
+    if (a.stamps && cta_lin < kStampCtas) g_dec_stamps[cta_lin * kStampPoints + point] = gtime_ns();
+  };
+  if (threadIdx.x == 0) stamp(0);  // CTA start
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t crank = S > 1 ? cluster_ctarank() : 0u;
@@ -181,7 +191,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       mbar_init(&empty[i], 1);
     }
     mbar_init(tmem_full, 1);
-    mbar_init(recv_bar, S > 1 ? (uint32_t)(S - 1) : 1u);
+    for (int i = 0; i < 4; ++i) mbar_init(&recv_bar[i], S > 1 ? (uint32_t)(S - 1) : 1u);
     *s_abort = 0;
     mbar_fence_init();
     // The first ring-full of W tiles is requested before anything else happens in
@@ -197,8 +207,11 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  // the peers' receive barriers exist before anyone can arrive on them
-  if (S > 1) cluster_sync_all();
+  // The peers' receive barriers must exist before anyone arrives on them: every thread
+  // arrives on the cluster barrier now and waits for it only where it first needs the
+  // peers (epilogue warps: before their first remote store; the others: before they leave),
+  // so the cluster-wide rendezvous is off the path to the first load and the first MMA.
+  if (S > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   const uint32_t tmem_base = *tmem_holder;
   auto fail = [&](uint32_t code) {
     *s_abort = 1;
@@ -213,7 +226,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       // dependency wait; the x tiles come after it.
       int pf_next = min(nkb, pre + a.l2_prefetch);
       for (int i = pre; i < pf_next; ++i) tma_prefetch_l2_2d(&map_w, kb_at(i) * kBlockK, tile * kBlockM);
+      stamp(1);  // prologue done, about to wait for the predecessor
       pdl_wait();
+      stamp(2);  // predecessor complete
       for (int i = 0; i < pre; ++i)
         tma_load_2d(tiles + (size_t)i * Cfg::kStageBytes + Cfg::kWBytes, &map_x, &full[i], kb_at(i) * kBlockK, 0);
       int stage = pre == stages ? 0 : pre;
@@ -237,8 +252,10 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           phase ^= 1u;
         }
       }
+      stamp(3);  // last load issued
       if (!ok) fail(GEMM_ERR_PRODUCER_WAIT);
     }
+    __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
       // -------------------------------------------------------------- MMA issuer
@@ -264,22 +281,27 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           phase ^= 1u;
         }
       }
+      stamp(4);  // last MMA issued
       if (ok)
         umma_commit(tmem_full);
       else
         fail(GEMM_ERR_MMA_WAIT);
     }
+    __syncwarp();
   } else {
     // ------------------------------------------------------------------ epilogue
     // Everything after the TMEM read works on shared memory with run-time loops:
     // the code stays small (an unrolled per-column epilogue costs more in
-    // instruction-cache misses than the whole GEMM takes).
+    // instruction-cache misses than the whole GEMM takes).  Each warp owns a
+    // quarter of the tile's rows from TMEM to the final store, so the four warps
+    // never wait for one another (except for the gate/up pairing).
     const int q = warp & 3;         // TMEM lane quarter of this warp
     const int row = q * 32 + lane;  // weight row inside the tile = output column
-    const int etid = (int)threadIdx.x - 64;
+    const bool silu = a.epi == DECODE_EPI_SILU_PAIRS;
     bool ok = mbar_wait_abortable(tmem_full, 0u, s_abort);
     if (!ok && lane == 0) fail(GEMM_ERR_EPILOGUE_WAIT);
-    ok = named_bar_all(3, 128, ok);  // the four warps stay together from here on
+    ok = __all_sync(0xffffffffu, ok);
+    if (q == 0 && lane == 0) stamp(5);  // accumulator complete
     tc_fence_after_sync();
     pdl_wait();  // this thread's stores come after everything the predecessor did
     // accumulator -> shared memory, column-major [BT columns][128 rows] fp32, in the
@@ -296,40 +318,52 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         for (int j = 0; j < 32; ++j) s_acc[(c * 32 + j) * kBlockM + row] = __uint_as_float(r[j]);
       }
     }
-    named_bar_sync(1, 128);
+    __syncwarp();
     const float4* s_acc4 = reinterpret_cast<const float4*>(s_acc);
-    if (ok && S > 1) {
-      // ---- hand every other CTA its slice of my partial: 16-byte stores, 512 B per warp ----
-      const uint32_t recv_local = smem_u32(s_recv);
-      for (int d = 0; d < S; ++d) {
-        if (d == (int)crank) continue;
-        const int lo = d * sl, hi = min(BT, lo + sl);
-        const int nvec = (hi - lo) * (kBlockM / 4);
-        const uint32_t remote =
-            map_to_cta(recv_local, (uint32_t)d) + (uint32_t)(decode_recv_slot((int)crank, d) * sl * kBlockM * 4);
-        for (int i = etid; i < nvec; i += 128) st_cluster_v4(remote + (uint32_t)i * 16u, s_acc4[lo * (kBlockM / 4) + i]);
+    if (S > 1) {
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // the peers' barriers exist
+      if (ok) {
+        // ---- hand every other CTA the rows of this warp of its column slice: a store
+        // instruction covers 4 columns x 128 bytes; then one release-arrive per peer ----
+        const uint32_t recv_local = smem_u32(s_recv);
+        const int rv = q * 8 + (lane & 7), cl = lane >> 3;  // float4 of my quarter, column within a group of 4
+        for (int d = 0; d < S; ++d) {
+          if (d == (int)crank) continue;
+          const int lo = d * sl, hi = min(BT, lo + sl);
+          const uint32_t remote =
+              map_to_cta(recv_local, (uint32_t)d) + (uint32_t)(decode_recv_slot((int)crank, d) * sl * kBlockM * 4);
+          for (int c = lo + cl; c < hi; c += 4)
+            st_cluster_v4(remote + (uint32_t)(((c - lo) * (kBlockM / 4) + rv) * 16), s_acc4[c * (kBlockM / 4) + rv]);
+        }
+        __syncwarp();
+        if (lane == 0) {
+          for (int d = 0; d < S; ++d)
+            if (d != (int)crank) mbar_arrive_cluster(map_to_cta(smem_u32(&recv_bar[q]), (uint32_t)d));
+        }
       }
-      fence_cluster();
-      named_bar_sync(1, 128);
-      if (etid == 0) {
-        for (int d = 0; d < S; ++d)
-          if (d != (int)crank) mbar_arrive_cluster(map_to_cta(smem_u32(recv_bar), (uint32_t)d));
-      }
-      ok = mbar_wait_cluster_abortable(recv_bar, 0u, s_abort);
-      if (!ok && lane == 0) fail(GEMM_ERR_EPILOGUE_WAIT);
-      ok = named_bar_all(3, 128, ok);
     }
+    if (silu) named_bar_sync(1, 128);  // gate rows meet the up rows another warp staged
+    if (ok && S > 1) {
+      // my rows of the peers' partials (gate/up pairing: every quarter)
+      for (int w = 0; w < 4; ++w) {
+        if (!silu && w != q) continue;
+        if (!mbar_wait_cluster_abortable(&recv_bar[w], 0u, s_abort)) ok = false;
+      }
+      if (!ok && lane == 0) fail(GEMM_ERR_EPILOGUE_WAIT);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (q == 0 && lane == 0) stamp(6);  // peers' partials received
     if (ok) {
       // ---- my slice: add the peers' partials in rank order, apply the epilogue, store.
-      // A work item is 8 consecutive rows (output columns) of one batch column.
+      // A work item is 8 consecutive rows (output columns) of one batch column; a warp takes the
+      // items of its own row quarter (gate/up: gate rows 16 q .. 16 q + 15 and their up rows).
       const int lo = (int)crank * sl, hi = min(min(BT, lo + sl), a.B);
-      const bool silu = a.epi == DECODE_EPI_SILU_PAIRS;
-      const int groups = silu ? 8 : 16;  // row groups per column (silu: gate rows only, the up rows ride along)
+      const int groups = silu ? 2 : 4;  // row groups of 8 per column in this warp's share
       const int n_out = silu ? a.N / 2 : a.N;
       const int n_tile0 = tile * (silu ? kBlockM / 2 : kBlockM);
       const bool vec_ok = (a.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.out) & 15u) == 0);
-      for (int idx = etid; idx < (hi - lo) * groups; idx += 128) {
-        const int j = lo + idx / groups, g = idx % groups;
+      for (int idx = lane; idx < (hi - lo) * groups; idx += 32) {
+        const int j = lo + idx / groups, g = q * groups + idx % groups;
         // sum over the cluster of rows r0 .. r0 + 7 of column j
         auto sum8 = [&](int r0, float (&acc)[8]) {
 #pragma unroll
@@ -370,8 +404,10 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
   }
   // ------------------------------------------------------------------- teardown
+  if (S > 1 && warp < 2) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 64) stamp(7);  // done
   pdl_wait();  // no thread leaves before the predecessor has finished
   if (warp == 1) {
     tc_fence_after_sync();
@@ -413,6 +449,11 @@ const int* decode_capacity(int sms) {
         t.cap[s] = n * s;
       else
         (void)cudaGetLastError();
+      // The cluster query counts one CTA per SM.  Measured (start stamps of every CTA): with
+      // shared memory for two CTAs per SM a second round of clusters becomes resident on
+      // the same SMs within 2-3 us, so twice that many CTAs run as ONE wave; beyond it the
+      // rest waits for the first CTAs to finish.
+      if (cfg.dynamicSmemBytes + 1024 <= ((size_t)228 << 10) / 2) t.cap[s] *= 2;
     }
   }
   tables[dev] = t;
@@ -459,6 +500,8 @@ cudaError_t launch_decode_bt(const void* x, const void* w, void* out, int B, int
   a.l2_ahead = env_ahead > 0 ? stages + env_ahead : 0;
   a.l2_prefetch = (w_bytes <= l2_budget) ? kb_per : env_ahead;
   a.k_stagger = env_stagger;
+  static const int env_stamps = getenv("PENNY_DEC_STAMPS") ? atoi(getenv("PENNY_DEC_STAMPS")) : 0;
+  a.stamps = env_stamps;
   rc = kernel_setup(reinterpret_cast<const void*>(gemm_decode_kernel<BT>), 227 << 10).rc;
   if (rc != cudaSuccess) return rc;
   return launch_kernel_ex(gemm_decode_kernel<BT>, dim3((unsigned)splits, (unsigned)tiles, 1), dim3(kDecThreads), smem,
@@ -478,12 +521,30 @@ cudaError_t launch_gemm_decode(const void* x, const void* w, void* out, int B, i
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (l2_budget_bytes < 0) l2_budget_bytes = (long long)48 << 20;
+  if (l2_budget_bytes < 0) l2_budget_bytes = (long long)32 << 20;
   if (B <= 32)
     return launch_decode_bt<32>(x, w, out, B, N, K, ldx, ldw, ldo, epi, splits, pdl, l2_budget_bytes, smem_kb, sms, error_word, stream);
   if (B <= 64)
     return launch_decode_bt<64>(x, w, out, B, N, K, ldx, ldw, ldo, epi, splits, pdl, l2_budget_bytes, smem_kb, sms, error_word, stream);
   return launch_decode_bt<128>(x, w, out, B, N, K, ldx, ldw, ldo, epi, splits, pdl, l2_budget_bytes, smem_kb, sms, error_word, stream);
+}
+
+int gemm_decode_stamps(unsigned long long* out, int max_ctas) {
+  const int n = std::min(max_ctas, kStampCtas);
+  if (cudaMemcpyFromSymbol(out, g_dec_stamps, (size_t)n * kStampPoints * sizeof(unsigned long long)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+int gemm_decode_capacity(int B, int splits) {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  (void)cudaGetLastError();
+  if (splits < 1 || splits > kDecodeMaxSplits) return 0;
+  const int* cap = B <= 32 ? decode_capacity<32>(sms) : (B <= 64 ? decode_capacity<64>(sms) : decode_capacity<128>(sms));
+  return cap[splits];
 }
 
 int gemm_decode_splits(int B, int N, int K) {

@@ -30,6 +30,13 @@ cudaError_t launch_gemm_decode(const void* x, const void* w, void* out, int B, i
                                int ldo, int epi, int splits, bool pdl, long long l2_budget_bytes,
                                int smem_kb, uint32_t* error_word, cudaStream_t stream);
 
+// Diagnostics (PENNY_DEC_STAMPS=1): copies the %globaltimer stamps of the last launch's first CTAs to
+// `out` ([ctas][8] nanoseconds: CTA start, prologue done, predecessor complete, last load issued, last
+// MMA issued, accumulator complete, peers' partials received, done) and returns the number of CTAs.
+int gemm_decode_stamps(unsigned long long* out, int max_ctas);
+
+// CTAs of the decode GEMM the current device holds at once when they come in clusters of `splits`.
+int gemm_decode_capacity(int B, int splits);
 // The cluster size launch_gemm_decode(splits = 0) uses for this shape on the current device.
 int gemm_decode_splits(int B, int N, int K);
 

@@ -12,6 +12,7 @@
 #include <cuda_runtime.h>
 
 #include "coll_args.h"
+#include "pdl.h"
 
 namespace penny {
 
@@ -20,6 +21,9 @@ struct LaunchCfg {
   int threads;
   cudaStream_t stream;
   int emu_world;  // 0: real launch; >0: emulate this many ranks on the current GPU
+  // real launches only: programmatic stream serialization, i.e. the kernel may become
+  // resident while its predecessor still runs; it waits for it before touching anything
+  bool pdl = false;
 };
 
 template <class Args>
@@ -29,6 +33,8 @@ struct EmuArgs {
 
 template <class Body, class Args>
 __global__ void __launch_bounds__(512) k_real(const CommCtx c, const Args a) {
+  pdl_launch_dependents();
+  pdl_wait();  // before the call counter is read and anything of the predecessor is touched
   const Blk b{(int)blockIdx.x, (int)gridDim.x, (int)blockDim.x};
   Body::run(c, c.rank, a, b);
 }
@@ -48,8 +54,8 @@ cudaError_t launch_body(const CommCtx& c, const Args* args, const LaunchCfg& cfg
   if (cfg.blocks < 1 || cfg.blocks > kMaxBlocks || cfg.threads < 32 || cfg.threads > 512)
     return cudaErrorInvalidConfiguration;
   if (cfg.emu_world <= 0) {
-    k_real<Body, Args><<<cfg.blocks, cfg.threads, 0, cfg.stream>>>(c, args[0]);
-    return cudaGetLastError();
+    return launch_kernel_ex(k_real<Body, Args>, dim3(cfg.blocks), dim3(cfg.threads), 0, cfg.stream, cfg.pdl, 1, c,
+                            args[0]);
   }
   EmuArgs<Args> ea;
   for (int r = 0; r < cfg.emu_world; ++r) ea.a[r] = args[r];

@@ -317,9 +317,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("comm_fused_ar_rmsnorm", [](int64_t h, std::vector<at::Tensor> in,
                                     std::vector<at::Tensor> residual, at::Tensor weight,
                                     std::vector<at::Tensor> out, std::vector<at::Tensor> residual_out,
-                                    double eps, int proto, int blocks, int threads, bool symmetric) {
+                                    double eps, int proto, int blocks, int threads, bool symmetric,
+                                    int symmetric_out_arg) {
     Communicator* c = as_comm(h);
     const int nv = c->views();
+    // symmetric: the inputs sit at one heap offset on every rank; symmetric_out: the outputs do
+    // (-1 = same answer as for the inputs)
+    const bool symmetric_out = symmetric_out_arg < 0 ? symmetric : symmetric_out_arg != 0;
     TORCH_CHECK((int)in.size() == nv && (int)out.size() == nv, "penny: expected ", nv, " tensor(s)");
     TORCH_CHECK(residual.empty() || (int)residual.size() == nv, "penny: residual views");
     TORCH_CHECK(residual_out.empty() || (int)residual_out.size() == nv, "penny: residual_out views");
@@ -360,10 +364,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     c->fused_ar_rmsnorm(dtype_of(in[0]), proto, ip.data(), residual.empty() ? nullptr : rp.data(),
                         weight.data_ptr(), op.data(), residual_out.empty() ? nullptr : rop.data(),
                         rows, hidden, (float)eps,
-                        make_tuning(blocks, threads, 1, 0, symmetric, symmetric), current_stream());
+                        make_tuning(blocks, threads, 1, 0, symmetric, symmetric_out), current_stream());
   }, py::arg("comm"), py::arg("inputs"), py::arg("residual"), py::arg("weight"),
      py::arg("outputs"), py::arg("residual_out"), py::arg("eps") = 1e-5, py::arg("proto") = 0,
-     py::arg("blocks") = 0, py::arg("threads") = 0, py::arg("symmetric") = false);
+     py::arg("blocks") = 0, py::arg("threads") = 0, py::arg("symmetric") = false,
+     py::arg("symmetric_out") = -1);
 
   // out = rmsnorm(x + residual) * weight without communication (world size 1)
   m.def("add_rmsnorm", [](at::Tensor x, c10::optional<at::Tensor> residual, at::Tensor weight,
@@ -536,6 +541,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.attr("PROTO_LL") = (int)FUSED_PROTO_LL;
   m.attr("PROTO_FLAG") = (int)FUSED_PROTO_FLAG;
   m.attr("PROTO_NVLS") = (int)FUSED_PROTO_NVLS;
+  m.attr("PROTO_NVLS_ONESHOT") = (int)FUSED_PROTO_NVLS_ONESHOT;
 
   bind_custom_all_reduce(m);
   bind_gemm(m);

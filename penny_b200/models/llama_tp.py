@@ -2,20 +2,27 @@
 
 One decode step for a batch of sequences on `world` GPUs:
 
-    embed -> [ rmsnorm -> qkv GEMM -> RoPE + KV append -> GQA decode attention
-               -> o_proj GEMM --(all-reduce + residual + rmsnorm, ONE kernel)-->
-               gate/up GEMM -> silu*mul -> down GEMM --(all-reduce + residual +
-               rmsnorm of the NEXT layer, one kernel)--> ] x layers
+    embed -> [ rmsnorm -> qkv GEMM -> (RoPE + KV append + GQA decode attention +
+               split merge, ONE kernel) -> o_proj GEMM --(all-reduce + residual +
+               rmsnorm, ONE kernel)--> gate/up GEMM with silu*mul in its epilogue
+               -> down GEMM --(all-reduce + residual + rmsnorm of the NEXT layer,
+               one kernel)--> ] x layers
           -> lm_head shard GEMM -> arg-max (local, then across ranks)
+
+Seven launches per layer, all of them this library's kernels: the linears are
+the tcgen05 decode GEMM (`ops.gemm_decode`; `linears="cublas"` swaps in
+torch.matmul for comparison), and every kernel is launched with programmatic
+stream serialization, so inside the captured CUDA graph a kernel's prologue and
+the loads of its constant operands (weights, old KV-cache rows) overlap the
+tail of the kernel before it.
 
 Column-parallel qkv / gate-up / lm_head, row-parallel o_proj / down (Megatron
 layout); 4 query heads + 1 KV head, 1792 FFN columns and 16032 vocabulary rows
 per GPU at TP=8.  The two all-reduces per layer are the fused kernels of this
 library (`backend="penny"`), or separate all-reduce + norm kernels
-(`"penny_unfused"`), or NCCL + norm (`"nccl"`, the baseline).  GEMMs go to
-cuBLAS; every other kernel is this library's.  The whole step is captured in a
-CUDA graph (the collectives keep their call counter in device memory, so the
-graph replays correctly).
+(`"penny_unfused"`), or NCCL + norm (`"nccl"`, the baseline).  The whole step is
+captured in a CUDA graph (the collectives keep their call counter in device
+memory, so the graph replays correctly).
 
 The reference has no model code: it is used by patching SGLang/vLLM
 (extra/sglang.patch, README.md:20-33).  This module is the stand-alone
@@ -58,10 +65,12 @@ class LlamaConfig:
 class LlamaTPDecoder:
     def __init__(self, cfg: LlamaConfig, comm=None, rank: int = 0, world: int = 1, max_batch: int = 64,
                  max_len: int = 2560, backend: str = "penny", proto: str = "auto", seed: int = 0,
-                 use_graph: bool = True, full_init: bool = False, process_group=None):
+                 use_graph: bool = True, full_init: bool = False, process_group=None, linears: str = "penny",
+                 pdl: bool = True):
         assert cfg.heads % world == 0 and cfg.kv_heads % world == 0 and cfg.ffn % world == 0
-        assert cfg.vocab % world == 0 and cfg.head_dim == 128
-        assert backend in ("penny", "penny_unfused", "nccl")
+        assert cfg.vocab % world == 0 and cfg.head_dim == 128 and (cfg.ffn // world) % 64 == 0
+        assert backend in ("penny", "penny_unfused", "nccl") and linears in ("penny", "cublas")
+        self.linears, self.pdl = linears, pdl
         if world > 1 and backend != "nccl":
             assert comm is not None, "a Communicator is required for the penny backends"
         self.cfg, self.comm, self.rank, self.world = cfg, comm, rank, world
@@ -85,7 +94,7 @@ class LlamaTPDecoder:
         self._init_weights(seed, full_init)
 
         def buf(*shape, dtype=dt, heap=False):
-            if heap and comm is not None and world > 1 and backend == "penny" and proto == "nvls":
+            if heap and comm is not None and world > 1 and backend == "penny" and proto in ("nvls", "nvls_oneshot"):
                 return comm.empty(*shape, dtype=dtype)
             return torch.empty(*shape, dtype=dtype, device=self.dev)
 
@@ -96,8 +105,11 @@ class LlamaTPDecoder:
         self.x = buf(B, H, heap=True)            # normalised activations (multicast target under NVLS)
         self.qkv = buf(B, (self.Hq + 2 * self.Hkv) * D)
         self.attn = buf(B, self.Hq * D)
-        self.part = buf(B, H, heap=True)         # row-parallel partial sums (switch-reduced under NVLS)
-        self.gu = buf(B, 2 * self.F)
+        # row-parallel partial sums (switch-reduced under NVLS): o_proj and down write different
+        # buffers, so consecutive all-reduces never read the same one
+        self.parts = [buf(B, H, heap=True), buf(B, H, heap=True)]
+        self.part = self.parts[0]
+        self.gu = buf(B, 2 * self.F) if linears == "cublas" else None
         self.act = buf(B, self.F)
         self.logits = buf(B, self.V)
         self.max_val = torch.empty(B, dtype=torch.float32, device=self.dev)
@@ -108,18 +120,22 @@ class LlamaTPDecoder:
         self.kcache = [torch.zeros(B, self.Hkv, max_len, D, dtype=dt, device=self.dev) for _ in range(cfg.layers)]
         self.vcache = [torch.zeros(B, self.Hkv, max_len, D, dtype=dt, device=self.dev) for _ in range(cfg.layers)]
         self.splits = max(1, min(16, -(-2 * 148 // (B * self.Hkv))))
-        self.workspace = torch.empty(ops.decode_attn_workspace_bytes(B, self.Hq, self.splits), dtype=torch.uint8,
-                                     device=self.dev)
+        # split partials + self-resetting arrival counters (zero before the first use)
+        self.workspace = torch.zeros(ops.decode_attn_fused_workspace_bytes(B, self.Hq, self.Hkv, self.splits),
+                                     dtype=torch.uint8, device=self.dev)
         self.scale = 1.0 / math.sqrt(D)
         self._graph = None
         self._host_in = torch.zeros(B, dtype=torch.int64).pin_memory()
         self._host_out = torch.zeros(B, dtype=torch.int64).pin_memory()
-        # kernels of this library launched per step (GEMMs and the few torch glue ops excluded)
-        per_layer = 1 + 2 + 1  # rope+append, attention (+merge), silu*mul; the 2 norms are counted below
+        # kernels of this library launched per step (the few torch glue ops excluded)
+        chunks = -(-B // 128)  # the decode GEMM takes up to 128 rows per launch
+        gemms = 4 * chunks if linears == "penny" else 0
+        per_layer = gemms + 1 + (1 if linears == "cublas" else 0)  # + fused attention (+ silu*mul beside cuBLAS)
         norms = 2 * cfg.layers + 1
         if backend == "penny_unfused" and world > 1:
             norms += 2 * cfg.layers  # separate all-reduce kernels
-        self.kernels_per_step = cfg.layers * per_layer + norms + 1 + (1 if world > 1 else 0)
+        self.kernels_per_step = (cfg.layers * per_layer + norms + 1 + (1 if world > 1 else 0)
+                                 + (chunks if linears == "penny" else 0))
 
     # ------------------------------------------------------------------ weights
     def _init_weights(self, seed: int, full_init: bool):
@@ -160,18 +176,35 @@ class LlamaTPDecoder:
                 gate = rnd(cfg.ffn, H, sub=base + 4)
                 up = rnd(cfg.ffn, H, sub=base + 5)
                 f = cfg.ffn // w
-                wgu = torch.cat([gate[r * f:(r + 1) * f], up[r * f:(r + 1) * f]]).contiguous()
+                wgu = self.interleave_gate_up(gate[r * f:(r + 1) * f], up[r * f:(r + 1) * f])
             else:
                 wqkv = rnd((self.Hq + 2 * self.Hkv) * D, H, sub=base * 64 + r + 1)
-                wgu = rnd(2 * self.F, H, sub=(base + 4) * 64 + r + 1)
-            self.layers.append(dict(
+                wgu = rnd(2 * self.F, H, sub=(base + 4) * 64 + r + 1)  # random: already "interleaved"
+            layer = dict(
                 wqkv=wqkv, wo=row_shard(H, cfg.heads * D, base + 3), wgu=wgu, wdown=row_shard(H, cfg.ffn, base + 6),
-                norm1=torch.ones(H, dtype=dt, device=self.dev), norm2=torch.ones(H, dtype=dt, device=self.dev)))
+                norm1=torch.ones(H, dtype=dt, device=self.dev), norm2=torch.ones(H, dtype=dt, device=self.dev))
+            if self.linears == "cublas":
+                layer["wgu_cat"] = torch.cat(self.split_gate_up(wgu)).contiguous()
+            self.layers.append(layer)
+
+    @staticmethod
+    def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+        """[F, H] gate and up -> the layout the fused silu*mul epilogue reads: blocks of 64 gate rows
+        followed by the 64 up rows of the same features."""
+        F, H = gate.shape
+        return torch.stack([gate.reshape(F // 64, 64, H), up.reshape(F // 64, 64, H)], 1).reshape(2 * F, H).contiguous()
+
+    @staticmethod
+    def split_gate_up(wgu: torch.Tensor):
+        """Inverse of interleave_gate_up: (gate [F, H], up [F, H])."""
+        F2, H = wgu.shape
+        v = wgu.view(F2 // 128, 2, 64, H)
+        return v[:, 0].reshape(F2 // 2, H), v[:, 1].reshape(F2 // 2, H)
 
     def weight_bytes(self) -> int:
         n = self.embed.numel() + self.lm_head.numel()
         for l in self.layers:
-            n += sum(l[k].numel() for k in ("wqkv", "wo", "wgu", "wdown"))
+            n += sum(l[k].numel() for k in ("wqkv", "wo", "wgu", "wdown"))  # wgu_cat (cuBLAS mode) is a copy
         return n * 2
 
     # ------------------------------------------------------------------- state
@@ -188,39 +221,58 @@ class LlamaTPDecoder:
         self.tokens.copy_(torch.randint(0, self.cfg.vocab, (self.B,), device=self.dev, generator=gt))
 
     # ----------------------------------------------------------------- the step
-    def _reduce_norm(self, weight):
-        """self.part (partial sums) -> self.x = rmsnorm(sum + residual) * weight; residual updated."""
+    def _reduce_norm(self, part, weight):
+        """part (partial sums) -> self.x = rmsnorm(sum + residual) * weight; residual updated."""
         if self.world == 1:
-            ops.add_rmsnorm(self.part, self.residual, weight, self.x, self.residual, self.cfg.eps)
+            ops.add_rmsnorm(part, self.residual, weight, self.x, self.residual, self.cfg.eps)
         elif self.backend == "penny":
-            self.comm.fused_all_reduce_rmsnorm(self.part, weight, residual=self.residual, out=self.x,
+            self.comm.fused_all_reduce_rmsnorm(part, weight, residual=self.residual, out=self.x,
                                                eps=self.cfg.eps, proto=self.proto)
         elif self.backend == "penny_unfused":
-            self.comm.all_reduce(self.part, out=self.part)
-            ops.add_rmsnorm(self.part, self.residual, weight, self.x, self.residual, self.cfg.eps)
+            self.comm.all_reduce(part, out=part)
+            ops.add_rmsnorm(part, self.residual, weight, self.x, self.residual, self.cfg.eps)
         else:
             import torch.distributed as dist
-            dist.all_reduce(self.part, group=self.pg)
-            ops.add_rmsnorm(self.part, self.residual, weight, self.x, self.residual, self.cfg.eps)
+            dist.all_reduce(part, group=self.pg)
+            ops.add_rmsnorm(part, self.residual, weight, self.x, self.residual, self.cfg.eps)
+
+    def _linear(self, x, w, out, silu_pairs=False, smem_kb=0):
+        """out = x @ w^T on this library's decode GEMM, 128 rows of x per launch."""
+        B = x.shape[0]
+        for r in range(0, B, 128):
+            ops.gemm_decode(x[r:r + 128], w, out[r:r + 128], silu_pairs, 0, self.pdl, -1, smem_kb)
 
     def _step_impl(self):
         cfg = self.cfg
         torch.index_select(self.embed, 0, self.tokens, out=self.residual)
         ops.add_rmsnorm(self.residual, None, self.layers[0]["norm1"], self.x, None, cfg.eps)
         for li, L in enumerate(self.layers):
-            torch.matmul(self.x, L["wqkv"].t(), out=self.qkv)
-            ops.rope_append(self.qkv, self.kcache[li], self.vcache[li], self.positions, self.Hq, self.Hkv,
-                            cfg.head_dim, cfg.rope_theta)
-            ops.decode_attention(self.qkv, self.kcache[li], self.vcache[li], self.positions, self.attn,
-                                 self.workspace, self.Hq, self.Hkv, self.splits, self.scale)
-            torch.matmul(self.attn, L["wo"].t(), out=self.part)
-            self._reduce_norm(L["norm2"])
-            torch.matmul(self.x, L["wgu"].t(), out=self.gu)
-            ops.silu_mul(self.gu, self.act)
-            torch.matmul(self.act, L["wdown"].t(), out=self.part)
+            if self.linears == "penny":
+                self._linear(self.x, L["wqkv"], self.qkv)
+            else:
+                torch.matmul(self.x, L["wqkv"].t(), out=self.qkv)
+            ops.decode_attention_fused(self.qkv, self.kcache[li], self.vcache[li], self.positions, self.attn,
+                                       self.workspace, self.Hq, self.Hkv, self.splits, self.scale, cfg.rope_theta,
+                                       self.pdl)
+            if self.linears == "penny":
+                self._linear(self.attn, L["wo"], self.parts[0])
+            else:
+                torch.matmul(self.attn, L["wo"].t(), out=self.parts[0])
+            self._reduce_norm(self.parts[0], L["norm2"])
+            if self.linears == "penny":
+                self._linear(self.x, L["wgu"], self.act, silu_pairs=True)
+                self._linear(self.act, L["wdown"], self.parts[1])
+            else:
+                torch.matmul(self.x, L["wgu_cat"].t(), out=self.gu)
+                ops.silu_mul(self.gu, self.act)
+                torch.matmul(self.act, L["wdown"].t(), out=self.parts[1])
             nxt = self.layers[li + 1]["norm1"] if li + 1 < cfg.layers else self.final_norm
-            self._reduce_norm(nxt)
-        torch.matmul(self.x, self.lm_head.t(), out=self.logits)
+            self._reduce_norm(self.parts[1], nxt)
+        if self.linears == "penny":
+            # nothing of the step needs to overlap with the LM head: give it the whole shared memory
+            self._linear(self.x, self.lm_head, self.logits, smem_kb=200)
+        else:
+            torch.matmul(self.x, self.lm_head.t(), out=self.logits)
         ops.argmax_rows(self.logits, self.max_val, self.max_idx, self.rank * self.V)
         if self.world == 1:
             self.next_tokens.copy_(self.max_idx)
@@ -323,8 +375,9 @@ class LlamaTPDecoder:
             attn = torch.stack(outs)
             res = res.to(torch.bfloat16).float() + (attn.to(torch.bfloat16).float() @ L["wo"].float().t())
             x = norm(res, L["norm2"])
-            gu = x.to(torch.bfloat16).float() @ L["wgu"].float().t()
-            act = torch.nn.functional.silu(gu[:, :cfg.ffn]) * gu[:, cfg.ffn:]
+            wg, wu = self.split_gate_up(L["wgu"])
+            xb = x.to(torch.bfloat16).float()
+            act = torch.nn.functional.silu(xb @ wg.float().t()) * (xb @ wu.float().t())
             res = res.to(torch.bfloat16).float() + (act.to(torch.bfloat16).float() @ L["wdown"].float().t())
             nxt = self.layers[li + 1]["norm1"] if li + 1 < cfg.layers else self.final_norm
             x = norm(res, nxt)

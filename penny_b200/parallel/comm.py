@@ -41,7 +41,7 @@ ALGOS = {
     "nvls_oneshot": ops.ALGO_NVLS_ONESHOT,
 }
 ALGO_NAMES = {v: k for k, v in ALGOS.items() if k not in ("ring",)}
-PROTOS = {"ll": ops.PROTO_LL, "flag": ops.PROTO_FLAG, "nvls": ops.PROTO_NVLS}
+PROTOS = {"ll": ops.PROTO_LL, "flag": ops.PROTO_FLAG, "nvls": ops.PROTO_NVLS, "nvls_oneshot": ops.PROTO_NVLS_ONESHOT}
 
 STATUS_NAMES = {
     0: "ok", 1: "timeout in a barrier", 2: "timeout waiting for data", 3: "timeout waiting for a credit",
@@ -234,7 +234,13 @@ class Communicator:
     def fused_all_reduce_rmsnorm(self, inp: TensorOrList, weight: torch.Tensor, residual: Optional[TensorOrList] = None,
                                  out: Optional[TensorOrList] = None, residual_out: Optional[TensorOrList] = None,
                                  eps: float = 1e-5, proto: str = "ll", blocks: int = 0, threads: int = 0):
-        """out = rmsnorm(all_reduce(inp) + residual) * weight; residual_out = all_reduce(inp) + residual."""
+        """out = rmsnorm(all_reduce(inp) + residual) * weight; residual_out = all_reduce(inp) + residual.
+
+        proto: "ll" (flag-in-data pushes, a handful of rows), "flag" (pushes + one flag barrier),
+        "nvls" (switch reduction, rows sharded over the ranks, result multicast: `inp` and `out`
+        must come from `empty()`; each rank keeps the residual of its own rows only) or
+        "nvls_oneshot" (every rank pulls all rows switch-reduced: `inp` from `empty()`, and
+        consecutive calls must alternate between two input buffers, see csrc/fused_ar_rmsnorm.cu)."""
         ins = self._as_list(inp)
         outs = self._as_list(out) if out is not None else [torch.empty_like(x) for x in ins]
         res = self._as_list(residual) if residual is not None else []
@@ -242,9 +248,8 @@ class Communicator:
             rout = self._as_list(residual_out)
         else:
             rout = res  # in place on the residual stream
-        sym = self.is_symmetric(ins) and self.is_symmetric(outs)
         ops.comm_fused_ar_rmsnorm(self._h, ins, res, weight, outs, rout, float(eps), PROTOS[proto],
-                                  blocks, threads, sym)
+                                  blocks, threads, self.is_symmetric(ins), int(self.is_symmetric(outs)))
         return self._ret(outs), (self._ret(rout) if rout else None)
 
     # ---------------------------------------------------------------------- MoE

@@ -32,6 +32,7 @@ CUDA_SOURCES = [
     "csrc/custom_all_reduce.cu",
     "csrc/comm.cu",
     "csrc/decode_kernels.cu",
+    "csrc/decode_attention_fused.cu",
     "csrc/gemm_sm100.cu",
     "csrc/gemm_fused_sm100.cu",
     "csrc/gemm_skinny_sm100.cu",

@@ -118,7 +118,7 @@ def main():
 
     # fused all-reduce + residual + RMSNorm
     hidden = 4096
-    protos = ["ll", "flag"] + (["nvls"] if comm.has_multicast else [])
+    protos = ["ll", "flag"] + (["nvls", "nvls_oneshot"] if comm.has_multicast else [])
     for rows in (1, 8, 64, 256):
         g = torch.Generator(device="cuda").manual_seed(77 + rank + rows)
         xin = (torch.randn(rows, hidden, device="cuda", generator=g) * 0.5).bfloat16()
@@ -134,6 +134,10 @@ def main():
                     xi = comm.empty(rows, hidden, dtype=torch.bfloat16)
                     xi.copy_(xin)
                     out = comm.empty(rows, hidden, dtype=torch.bfloat16)
+                elif proto == "nvls_oneshot":  # a fresh input buffer per call: consecutive calls never share one
+                    xi = comm.empty(rows, hidden, dtype=torch.bfloat16)
+                    xi.copy_(xin)
+                    out = torch.empty_like(xin)
                 else:
                     xi, out = xin, torch.empty_like(xin)
                 r = res.clone()
@@ -203,7 +207,7 @@ def main():
         B, kv = 4, 100
         full = LlamaTPDecoder(cfg, world=1, max_batch=B, max_len=160, use_graph=False, full_init=True)
         full.fill_synthetic_kv(kv)
-        protos = ["ll", "flag"] + (["nvls"] if comm.has_multicast else [])
+        protos = ["ll", "flag"] + (["nvls", "nvls_oneshot"] if comm.has_multicast else [])
         for backend, proto in [("penny", p) for p in protos] + [("penny_unfused", "flag"), ("nccl", "flag")]:
             tp = LlamaTPDecoder(cfg, comm=comm, rank=rank, world=world, max_batch=B, max_len=160,
                                 backend=backend, proto=proto, use_graph=(backend != "nccl"), full_init=True)

@@ -47,6 +47,75 @@ def test_rope_append_and_attention():
             torch.testing.assert_close(out[b].float(), want, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("pdl", [False, True])
+def test_fused_attention_matches_separate_kernels_and_fp32(pdl):
+    """rope + KV append + attention + split merge in one launch: same cache rows, same
+    output as the three separate kernels and as the fp32 oracle; called twice (the arrival
+    counters reset themselves), empty cache included (position 0)."""
+    from penny_b200._ext import ops
+    torch.manual_seed(3)
+    theta = 500000.0
+    for B, Hq, Hkv in ((5, 8, 2), (3, 4, 4), (2, 8, 1)):
+        D, L = 128, 300
+        G = Hq // Hkv
+        pos = torch.tensor([0, 31, 32, 200, 298][:B], dtype=torch.int32, device="cuda")
+        for splits in (1, 3, 8):
+            ws = torch.zeros(ops.decode_attn_fused_workspace_bytes(B, Hq, Hkv, splits), dtype=torch.uint8, device="cuda")
+            for rep in range(2):
+                qkv = torch.randn(B, (Hq + 2 * Hkv) * D, device="cuda").bfloat16()
+                kc = torch.randn(B, Hkv, L, D, device="cuda").bfloat16()
+                vc = torch.randn(B, Hkv, L, D, device="cuda").bfloat16()
+                # the three-kernel path on copies
+                qkv2, kc2, vc2 = qkv.clone(), kc.clone(), vc.clone()
+                ops.rope_append(qkv2, kc2, vc2, pos, Hq, Hkv, D, theta)
+                out2 = torch.empty(B, Hq * D, device="cuda", dtype=torch.bfloat16)
+                ws2 = torch.empty(ops.decode_attn_workspace_bytes(B, Hq, splits), dtype=torch.uint8, device="cuda")
+                ops.decode_attention(qkv2, kc2, vc2, pos, out2, ws2, Hq, Hkv, splits, 1.0 / math.sqrt(D))
+                # the fused kernel
+                out = torch.full((B, Hq * D), float("nan"), device="cuda", dtype=torch.bfloat16)
+                ops.decode_attention_fused(qkv, kc, vc, pos, out, ws, Hq, Hkv, splits, 1.0 / math.sqrt(D), theta, pdl)
+                torch.cuda.synchronize()
+                assert torch.equal(kc, kc2) and torch.equal(vc, vc2)  # same rows appended, nothing else touched
+                torch.testing.assert_close(out.float(), out2.float(), atol=2e-2, rtol=2e-2)
+                for b in range(B):
+                    p = int(pos[b]) + 1
+                    q = qkv2[b, :Hq * D].view(Hkv, G, D).float()
+                    s = torch.einsum("hgd,htd->hgt", q, kc[b, :, :p].float()) / math.sqrt(D)
+                    want = torch.einsum("hgt,htd->hgd", s.softmax(-1), vc[b, :, :p].float()).reshape(Hq * D)
+                    torch.testing.assert_close(out[b].float(), want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("linears", ["penny", "cublas"])
+def test_decoder_linears_agree(linears):
+    """The decoder on this library's decode GEMM (default) and on cuBLAS produce the same logits."""
+    from penny_b200.models.llama_tp import LlamaConfig, LlamaTPDecoder
+    cfg = LlamaConfig.tiny()
+    m = LlamaTPDecoder(cfg, world=1, max_batch=6, max_len=200, use_graph=True, full_init=True, linears=linears)
+    m.fill_synthetic_kv(150)
+    m.capture()
+    tokens, positions = m.tokens.clone(), m.positions.clone()
+    m.step_device()
+    torch.cuda.synchronize()
+    want = m.reference_logits(tokens, positions, m.kcache, m.vcache)
+    err = (m.logits.float() - want).abs().max().item()
+    assert err < 0.05 * want.std().item() + 0.02, (linears, err)
+
+
+def test_decoder_batch_above_128_rows():
+    """More than 128 rows: the decode GEMM runs once per 128 rows."""
+    from penny_b200.models.llama_tp import LlamaConfig, LlamaTPDecoder
+    cfg = LlamaConfig.tiny()
+    m = LlamaTPDecoder(cfg, world=1, max_batch=160, max_len=64, use_graph=True, full_init=True)
+    m.fill_synthetic_kv(20)
+    m.capture()
+    tokens, positions = m.tokens.clone(), m.positions.clone()
+    m.step_device()
+    torch.cuda.synchronize()
+    want = m.reference_logits(tokens, positions, m.kcache, m.vcache)
+    err = (m.logits.float() - want).abs().max().item()
+    assert err < 0.05 * want.std().item() + 0.02, err
+
+
 def test_silu_mul_and_argmax():
     from penny_b200._ext import ops
     torch.manual_seed(1)
