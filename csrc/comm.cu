@@ -136,15 +136,32 @@ LaunchCfg Communicator::cfg_for(size_t vecs, const Tuning& t, cudaStream_t s, in
   return cfg;
 }
 
-int Communicator::pick_algo(int dtype, size_t n) const {
+void Communicator::set_tuning(int elem_size, bool symmetric, const std::vector<TuneEntry>& entries) {
+  tune_[elem_size == 4 ? 1 : 0][symmetric ? 1 : 0] = entries;
+}
+
+int Communicator::pick_algo(int dtype, size_t n, bool symmetric) const {
   const size_t bytes = n * (size_t)dtype_size(dtype);
   if (world_ < 2) return ALGO_ONESHOT;
   const bool even = (world_ == 2 || world_ == 4 || world_ == 6 || world_ == 8);
   if (!even) return ALGO_RING_STANDARD;
-  // Measured on 8 x B200 (device time per call inside a CUDA graph): the
-  // flag-in-data protocol wins up to 32 KiB (9-11 us), the switch reduction from
-  // there on (17 us at 256 KiB, 826 GB/s bus bandwidth at 1 GiB); without a
-  // multicast mapping the pushes take over (one-shot to 256 KiB, then two-shot).
+  const std::vector<TuneEntry>& table = tune_[dtype_size(dtype) == 4 ? 1 : 0][symmetric ? 1 : 0];
+  if (!table.empty()) {
+    int algo = table.back().algo;
+    for (const TuneEntry& e : table) {
+      if (bytes <= e.max_bytes) {
+        algo = e.algo;
+        break;
+      }
+    }
+    const bool needs_mc = algo == ALGO_NVLS || algo == ALGO_NVLS_ONESHOT;
+    if (!needs_mc || has_multicast()) return algo;
+    return bytes <= ((size_t)256 << 10) ? ALGO_ONESHOT : ALGO_TWOSHOT;
+  }
+  // No table installed.  Measured on 8 x B200 (device time per call inside a CUDA
+  // graph): the flag-in-data protocol wins up to 32 KiB (9-11 us), the switch
+  // reduction from there on (17 us at 256 KiB, 826 GB/s bus bandwidth at 1 GiB);
+  // without a multicast mapping the pushes take over (one-shot to 256 KiB, then two-shot).
   if (bytes <= (size_t)32 << 10) return ALGO_ONESHOT_LL;
   if (has_multicast()) return ALGO_NVLS;
   if (bytes <= (size_t)256 << 10) return ALGO_ONESHOT;
@@ -160,7 +177,7 @@ void Communicator::all_reduce(int algo, int dtype, const void* const* in, void* 
       ckrt(cudaMemcpyAsync(out[0], in[0], n * es, cudaMemcpyDeviceToDevice, stream), "memcpy");
     return;
   }
-  if (algo == ALGO_AUTO) algo = pick_algo(dtype, n);
+  if (algo == ALGO_AUTO) algo = pick_algo(dtype, n, t.symmetric_in && t.symmetric_out);
   if ((algo == ALGO_NVLS || algo == ALGO_NVLS_ONESHOT) && !has_multicast())
     throw std::runtime_error("penny: NVLS all-reduce requested but the heap has no multicast (" +
                              heap_->multicast_note() + ")");

@@ -105,9 +105,19 @@ class Communicator {
   void all_gather_gemm(const void* a_shard, const void* b, void* out, int M, int N, int K, int lda,
                        int ldb, int ldc, int side_ctas, uint32_t* error_word, cudaStream_t stream);
 
-  // Largest n an all-reduce algorithm can take in one launch with the scratch
-  // the heap can still provide (the host splits larger messages).
-  int pick_algo(int dtype, size_t n) const;
+  // The all-reduce algorithm `auto` resolves to.  A measured table (set_tuning)
+  // for this element size and memory class decides when there is one: the first
+  // entry whose byte bound is >= the message size, the last entry beyond.  Without
+  // a table a two-threshold rule from 8-GPU measurements is used.  symmetric:
+  // both tensors sit at one heap offset on every rank (the switch and the peers
+  // can address them directly); otherwise the NVLS algorithms pay staging copies.
+  int pick_algo(int dtype, size_t n, bool symmetric = false) const;
+  struct TuneEntry {
+    size_t max_bytes;  // inclusive upper bound; ~0 for the last entry
+    int algo;
+  };
+  // Installs the all-reduce table of (elem_size 2 or 4, symmetric or not).  Entries sorted by bound.
+  void set_tuning(int elem_size, bool symmetric, const std::vector<TuneEntry>& entries);
 
   // Provokes a device-side timeout on a private flag (nothing else is touched).
   void wait_selftest(cudaStream_t stream);
@@ -146,6 +156,7 @@ class Communicator {
   // gathered A of all_gather_gemm: one dedicated region per (M, K), kept for the
   // communicator's lifetime and reused, so alternating shapes do not grow the heap
   std::map<std::pair<int, int>, Region> ag_regions_;
+  std::vector<TuneEntry> tune_[2][2];  // [elem_size == 4][symmetric]
   bool destroyed_ = false;
 };
 

@@ -221,7 +221,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("comm_barrier", [](int64_t h) { as_comm(h)->host_barrier(); });
   m.def("comm_poison_scratch", [](int64_t h) { as_comm(h)->poison_scratch(); });
   m.def("comm_set_timeout_ms", [](int64_t h, int ms) { as_comm(h)->set_timeout_ms(ms); });
-  m.def("comm_pick_algo", [](int64_t h, int dtype, int64_t n) { return as_comm(h)->pick_algo(dtype, (size_t)n); });
+  m.def("comm_pick_algo", [](int64_t h, int dtype, int64_t n, bool symmetric) {
+    return as_comm(h)->pick_algo(dtype, (size_t)n, symmetric);
+  }, py::arg("comm"), py::arg("dtype"), py::arg("n"), py::arg("symmetric") = false);
+  // all-reduce table of one (element size, memory class): [(max_bytes or -1 for "and above", algo id), ...]
+  m.def("comm_set_tuning", [](int64_t h, int elem_size, bool symmetric, std::vector<std::pair<int64_t, int>> rows) {
+    std::vector<Communicator::TuneEntry> e;
+    for (auto& r : rows) e.push_back({r.first < 0 ? ~(size_t)0 : (size_t)r.first, r.second});
+    as_comm(h)->set_tuning(elem_size, symmetric, e);
+  });
 
   // A tensor whose storage is a fresh symmetric allocation.  In emulation one
   // tensor per virtual rank is returned (all at the same heap offset).

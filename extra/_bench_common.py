@@ -40,7 +40,7 @@ class Recorder:
 
     def close(self):
         if self.rank == 0 and self.out:
-            with open(self.out, "w") as f:
+            with open(self.out, "a") as f:
                 for r in self.rows:
                     f.write(json.dumps(r) + "\n")
 

@@ -15,9 +15,10 @@ from _bench_common import DTYPES, NVLINK_GBS, Recorder, base_parser, uniform
 from penny_b200.utils import bench_device, bus_bandwidth_gbs, initialize_distributed, shutdown
 
 
-def main():
-    args = base_parser().parse_args()
-    rank, world, comm = initialize_distributed(heap_bytes=int(args.heap_gib * (1 << 30)))
+def main(argv=None, ctx=None):
+    """ctx: (rank, world, comm) of an already initialised process (extra/sweep_all.py); else set up here."""
+    args = base_parser().parse_args(argv)
+    rank, world, comm = ctx if ctx is not None else initialize_distributed(heap_bytes=int(args.heap_gib * (1 << 30)))
     dtype = DTYPES[args.dtype]
     es = torch.empty((), dtype=dtype).element_size()
     rec = Recorder(rank, args.out)
@@ -47,12 +48,26 @@ def main():
             out = sym_out if direct else torch.empty(n * world, device="cuda", dtype=dtype)
             comm.all_gather(x, out=out, nvls=nvls)
             comm.check()
+            algo = "nvls" if nvls else "push"   # the name the tuner table uses; `direct` is the memory class
             if not torch.equal(out, ref):
                 raise SystemExit(f"rank {rank}: all_gather/{name} @ {shard_bytes} B differs from NCCL")
             t = bench_device(lambda: comm.all_gather(x, out=out, nvls=nvls), args.warmup, args.num_tests)["median_us"]
             bw = bus_bandwidth_gbs("all_gather", total, world, t)
-            rec.add(op="all_gather", impl="penny", algo=name, world=world, dtype=args.dtype, shard_bytes=shard_bytes,
+            rec.add(op="all_gather", impl="penny", algo=algo, variant=name, world=world, dtype=args.dtype,
+                    bytes=shard_bytes, shard_bytes=shard_bytes, symmetric=direct,
                     t_us=round(t, 2), busbw_gbs=round(bw, 2), frac_nvlink=round(bw / NVLINK_GBS, 4),
+                    vs_nccl=round(nccl_us / t, 3) if nccl_us else None)
+        # what `algo="auto"` (the measured table) makes of it, for both kinds of output tensor
+        for direct in ([False, True] if sym_out is not None else [False]):
+            out = sym_out if direct else torch.empty(n * world, device="cuda", dtype=dtype)
+            comm.all_gather(x, out=out)
+            comm.check()
+            if not torch.equal(out, ref):
+                raise SystemExit(f"rank {rank}: all_gather/auto @ {shard_bytes} B differs from NCCL")
+            t = bench_device(lambda: comm.all_gather(x, out=out), args.warmup, args.num_tests)["median_us"]
+            bw = bus_bandwidth_gbs("all_gather", total, world, t)
+            rec.add(op="all_gather", impl="penny", algo="auto", world=world, dtype=args.dtype, bytes=shard_bytes,
+                    shard_bytes=shard_bytes, symmetric=direct, t_us=round(t, 2), busbw_gbs=round(bw, 2),
                     vs_nccl=round(nccl_us / t, 3) if nccl_us else None)
         if not car.disabled and total < car.max_size and shard_bytes % 16 == 0:
             out = car.custom_all_gather(x)
@@ -64,7 +79,8 @@ def main():
     comm.check()
     rec.close()
     car.close()
-    shutdown()
+    if ctx is None:
+        shutdown()
 
 
 if __name__ == "__main__":

@@ -29,7 +29,7 @@ from penny_b200.utils import bench_device, bench_graph, bus_bandwidth_gbs, initi
 NVLINK_GBS = 900.0
 
 
-def parse():
+def parse(argv=None):
     p = argparse.ArgumentParser()
     p.add_argument("--algo", nargs="*", default=["all"], help="names or the reference's ids 0-3; 'all'; 'auto'")
     p.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32"])
@@ -49,18 +49,22 @@ def parse():
     p.add_argument("--graph-inner", type=int, default=10,
                    help="also time N back-to-back calls inside one CUDA graph (sizes <= 8 MiB); 0 = off")
     p.add_argument("--out", default="")
-    return p.parse_args()
+    p.add_argument("--max-slow-mib", type=int, default=256,
+                   help="largest message (MiB) for the parity algorithms (simple ring, tree, double ring)")
+    return p.parse_args(argv)
 
 
-def main():
-    args = parse()
-    rank, world, comm = initialize_distributed(heap_bytes=int(args.heap_gib * (1 << 30)))
+def main(argv=None, ctx=None):
+    """ctx: (rank, world, comm) of an already initialised process (extra/sweep_all.py); else set up here."""
+    args = parse(argv)
+    rank, world, comm = ctx if ctx is not None else initialize_distributed(heap_bytes=int(args.heap_gib * (1 << 30)))
     dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]
     es = torch.empty((), dtype=dtype).element_size()
     names = []
     for a in args.algo:
         if a == "all":
-            names += ["oneshot_ll", "oneshot", "twoshot", "ring_simple", "ring_standard", "double_ring", "tree"]
+            names += ["oneshot_ll", "oneshot", "twoshot", "twoshot_pipelined", "ring_simple", "ring_standard",
+                      "double_ring", "tree"]
             if comm.has_multicast:
                 names += ["nvls_oneshot", "nvls"]
             names += ["auto"]
@@ -125,8 +129,10 @@ def main():
                 continue
             if name in ("oneshot", "nvls_oneshot") and nbytes > (32 << 20):
                 continue
-            if name in ("ring_simple", "tree", "double_ring") and nbytes > (256 << 20):
+            if name in ("ring_simple", "tree", "double_ring") and nbytes > (args.max_slow_mib << 20):
                 continue
+            if name == "twoshot_pipelined" and nbytes < (1 << 20):
+                continue  # a pipeline over pieces of a chunk: nothing to overlap below that
             nnodes = args.nnodes if name in ("double_ring", "tree", "ring_standard") else 1
             if name in ("double_ring", "tree") and nnodes == 1 and world >= 4:
                 nnodes = 2
@@ -160,7 +166,7 @@ def main():
             rec = {"op": "all_reduce", "impl": "penny", "algo": name, "world": world, "dtype": args.dtype,
                    "bytes": nbytes, "t_us": round(t, 2), "busbw_gbs": round(bw, 2),
                    "frac_nvlink": round(bw / NVLINK_GBS, 4), "symmetric": args.symmetric,
-                   "picked": comm.pick_algo(dtype, n) if name == "auto" else name}
+                   "picked": comm.pick_algo(dtype, n, args.symmetric) if name == "auto" else name}
             if args.tune:
                 rec["blocks"], rec["threads"] = blocks, threads
             if nccl_us:
@@ -191,12 +197,13 @@ def main():
         if rank == 0:
             prof.export_chrome_trace("trace_penny.json")
     if rank == 0 and args.out:
-        with open(args.out, "w") as f:
+        with open(args.out, "a") as f:
             for r in results:
                 f.write(json.dumps(r) + "\n")
     if custom is not None:
         custom.close()
-    shutdown()
+    if ctx is None:
+        shutdown()
 
 
 if __name__ == "__main__":

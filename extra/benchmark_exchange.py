@@ -17,12 +17,13 @@ from _bench_common import DTYPES, NVLINK_GBS, Recorder, base_parser, uniform
 from penny_b200.utils import bench_device, initialize_distributed, shutdown
 
 
-def main():
+def main(argv=None, ctx=None):
+    """ctx: (rank, world, comm) of an already initialised process (extra/sweep_all.py); else set up here."""
     p = base_parser(default_start=12, default_range=15)
     p.add_argument("--mode", default="intranode", choices=["intranode", "internode"])
     p.add_argument("--all-to-all", action="store_true")
-    args = p.parse_args()
-    rank, world, comm = initialize_distributed(heap_bytes=int(args.heap_gib * (1 << 30)))
+    args = p.parse_args(argv)
+    rank, world, comm = ctx if ctx is not None else initialize_distributed(heap_bytes=int(args.heap_gib * (1 << 30)))
     dtype = DTYPES[args.dtype]
     es = torch.empty((), dtype=dtype).element_size()
     rec = Recorder(rank, args.out)
@@ -63,29 +64,23 @@ def main():
             dist.all_to_all_single(ref, xs)
             t_nccl = None if args.no_nccl else bench_device(lambda: dist.all_to_all_single(ref, xs), args.warmup,
                                                             args.num_tests)["median_us"]
-            out = comm.all_to_all(xs)
-            comm.check()
-            if not torch.equal(out, ref):
-                raise SystemExit(f"rank {rank}: all_to_all @ {nbytes} B per peer differs from NCCL")
-            t = bench_device(lambda: comm.all_to_all(xs, out=out), args.warmup, args.num_tests)["median_us"]
             sent = nbytes * (world - 1)
-            rec.add(op="all_to_all", impl="penny", world=world, dtype=args.dtype, bytes_per_peer=nbytes,
-                    t_us=round(t, 2), egress_gbs=round(sent / t / 1e3, 2),
-                    frac_nvlink=round(sent / t / 1e3 / NVLINK_GBS, 4),
-                    nccl_us=round(t_nccl, 2) if t_nccl else None, vs_nccl=round(t_nccl / t, 3) if t_nccl else None)
-            if os.environ.get("PENNY_A2A_PIPELINED", "0") == "1":   # opt-in until it has been timed on hardware
-                out2 = comm.all_to_all(xs, pipelined=True)
+            for name in ("push", "pipelined", "auto"):
+                if name == "pipelined" and nbytes < (64 << 10):
+                    continue
+                out = comm.all_to_all(xs, algo=name)
                 comm.check()
-                if not torch.equal(out2, ref):
-                    raise SystemExit(f"rank {rank}: pipelined all_to_all @ {nbytes} B per peer differs from NCCL")
-                t = bench_device(lambda: comm.all_to_all(xs, out=out2, pipelined=True), args.warmup,
-                                 args.num_tests)["median_us"]
-                rec.add(op="all_to_all", impl="penny", algo="pipelined", world=world, dtype=args.dtype,
-                        bytes_per_peer=nbytes, t_us=round(t, 2), egress_gbs=round(sent / t / 1e3, 2),
-                        vs_nccl=round(t_nccl / t, 3) if t_nccl else None)
+                if not torch.equal(out, ref):
+                    raise SystemExit(f"rank {rank}: all_to_all/{name} @ {nbytes} B per peer differs from NCCL")
+                t = bench_device(lambda: comm.all_to_all(xs, out=out, algo=name), args.warmup, args.num_tests)["median_us"]
+                rec.add(op="all_to_all", impl="penny", algo=name, world=world, dtype=args.dtype, bytes=nbytes,
+                        bytes_per_peer=nbytes, symmetric=False, t_us=round(t, 2), egress_gbs=round(sent / t / 1e3, 2),
+                        frac_nvlink=round(sent / t / 1e3 / NVLINK_GBS, 4),
+                        nccl_us=round(t_nccl, 2) if t_nccl else None, vs_nccl=round(t_nccl / t, 3) if t_nccl else None)
     comm.check()
     rec.close()
-    shutdown()
+    if ctx is None:
+        shutdown()
 
 
 if __name__ == "__main__":

@@ -8,8 +8,6 @@ and the drop-in CustomAllreduce.reduce_scatter (<= 8 MiB inputs).  Bus bandwidth
 = (n-1)/n * input_bytes / t.  Counterpart of the reference's
 extra/benchmark_reduce_scatter.py.
 """
-import os
-
 import torch
 import torch.distributed as dist
 
@@ -17,9 +15,10 @@ from _bench_common import DTYPES, NVLINK_GBS, Recorder, base_parser, uniform
 from penny_b200.utils import bench_device, bus_bandwidth_gbs, initialize_distributed, shutdown
 
 
-def main():
-    args = base_parser().parse_args()
-    rank, world, comm = initialize_distributed(heap_bytes=int(args.heap_gib * (1 << 30)))
+def main(argv=None, ctx=None):
+    """ctx: (rank, world, comm) of an already initialised process (extra/sweep_all.py); else set up here."""
+    args = base_parser().parse_args(argv)
+    rank, world, comm = ctx if ctx is not None else initialize_distributed(heap_bytes=int(args.heap_gib * (1 << 30)))
     dtype = DTYPES[args.dtype]
     es = torch.empty((), dtype=dtype).element_size()
     rec = Recorder(rank, args.out)
@@ -47,10 +46,11 @@ def main():
             rec.add(op="reduce_scatter", impl="nccl", world=world, dtype=args.dtype, shard_bytes=shard_bytes,
                     t_us=round(nccl_us, 2), busbw_gbs=round(bus_bandwidth_gbs("reduce_scatter", total, world, nccl_us), 2))
         variants = [("push", False, False)]
-        if os.environ.get("PENNY_RS_PIPELINED", "0") == "1":
-            variants.append(("push_pipelined", False, True))   # opt-in until it has been timed on hardware
+        if shard_bytes >= (256 << 10):
+            variants.append(("pipelined", False, True))
         if comm.has_multicast and shard_bytes % 16 == 0:
             variants.append(("nvls", True, False))
+        variants.append(("auto", None, None))
         out = torch.empty(shard, device="cuda", dtype=dtype)
         for name, nvls, pipe in variants:
             comm.reduce_scatter(x, out=out, nvls=nvls, pipelined=pipe)
@@ -61,7 +61,7 @@ def main():
                              args.num_tests)["median_us"]
             bw = bus_bandwidth_gbs("reduce_scatter", total, world, t)
             rec.add(op="reduce_scatter", impl="penny", algo=name, world=world, dtype=args.dtype,
-                    shard_bytes=shard_bytes, t_us=round(t, 2), busbw_gbs=round(bw, 2),
+                    bytes=shard_bytes, shard_bytes=shard_bytes, t_us=round(t, 2), busbw_gbs=round(bw, 2),
                     frac_nvlink=round(bw / NVLINK_GBS, 4), symmetric=args.symmetric,
                     vs_nccl=round(nccl_us / t, 3) if nccl_us else None)
         if not car.disabled and total < car.max_size and shard_bytes % 16 == 0:
@@ -74,7 +74,8 @@ def main():
     comm.check()
     rec.close()
     car.close()
-    shutdown()
+    if ctx is None:
+        shutdown()
 
 
 if __name__ == "__main__":

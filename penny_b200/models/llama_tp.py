@@ -82,9 +82,11 @@ class LlamaTPDecoder:
         dt = torch.bfloat16
         D, H = cfg.head_dim, cfg.hidden
         if proto == "auto":
-            # flag-in-data lines for a handful of rows, the switch (when bound) or
-            # flag barriers beyond that
-            if max_batch <= 16:
+            # the measured table when it covers this shape, else: flag-in-data lines for a handful of
+            # rows, the switch (when bound) or flag barriers beyond that
+            if comm is not None and world > 1 and hasattr(comm, "pick_fused_proto"):
+                proto = comm.pick_fused_proto(max_batch, H, dt)
+            elif max_batch <= 16:
                 proto = "ll"
             elif comm is not None and getattr(comm, "has_multicast", False):
                 proto = "nvls"

@@ -23,6 +23,7 @@ import torch
 
 from .._ext import ops
 from ..config import PennyConfig
+from .tuner import Tuner
 
 TensorOrList = Union[torch.Tensor, Sequence[torch.Tensor]]
 
@@ -81,6 +82,26 @@ class Communicator:
         self._symmetric = {}
         # PennyConfig.debug_poison: check() also overwrites all scratch with NaN patterns
         self.debug_poison = False
+        # measured (op, world, dtype, memory class, size) -> algorithm table; its all-reduce rows
+        # also go to the native communicator, so "auto" means the same through every entry point
+        self.tuner = Tuner.load()
+        self._install_tuning()
+
+    def _install_tuning(self):
+        for es, dt in ((2, "bf16"), (4, "fp32")):
+            for sym in (False, True):
+                rows = self.tuner.rows("all_reduce", self.world_size, dt, sym)
+                if not rows:
+                    continue
+                try:
+                    ops.comm_set_tuning(self._h, es, sym, [(-1 if b is None else int(b), ALGOS[a]) for b, a in rows])
+                except KeyError:
+                    continue  # a table naming an algorithm this build does not have: keep the native rule
+
+    def set_tuner(self, tuner: Tuner):
+        """Replaces the algorithm table (e.g. one just built by Tuner.from_sweep)."""
+        self.tuner = tuner
+        self._install_tuning()
 
     # ------------------------------------------------------------------ creation
     @classmethod
@@ -151,9 +172,33 @@ class Communicator:
     def set_timeout_ms(self, ms: int):
         ops.comm_set_timeout_ms(self._h, int(ms))
 
-    def pick_algo(self, dtype: torch.dtype, numel: int) -> str:
+    def pick_algo(self, dtype: torch.dtype, numel: int, symmetric: bool = False) -> str:
+        """The all-reduce algorithm `algo="auto"` resolves to for this message."""
+        forced = os.environ.get("PENNY_ALGO")
+        if forced:
+            return forced
         dt = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[dtype]
-        return ALGO_NAMES[ops.comm_pick_algo(self._h, dt, int(numel))]
+        return ALGO_NAMES[ops.comm_pick_algo(self._h, dt, int(numel), bool(symmetric))]
+
+    def _pick(self, op: str, nbytes: int, dtype, symmetric: bool) -> Optional[str]:
+        return self.tuner.pick(op, nbytes, self.world_size, dtype, symmetric, self.has_multicast)
+
+    def pick_fused_proto(self, rows: int, hidden: int, dtype=torch.bfloat16, symmetric_in: bool = True,
+                         symmetric_out: bool = True) -> str:
+        """Transport of fused_all_reduce_rmsnorm(proto="auto"): the measured table when it has an
+        entry that these tensors allow, else a handful of rows -> flag-in-data lines, heap tensors ->
+        the switch, anything else -> pushes + a flag barrier."""
+        nbytes = rows * hidden * torch.empty((), dtype=dtype).element_size()
+        mc = self.has_multicast and not self.emulated
+
+        def allowed(p):
+            return p in ("ll", "flag") or (mc and symmetric_in and (symmetric_out or p == "nvls_oneshot"))
+        p = self._pick("fused_norm", nbytes, dtype, symmetric_in)
+        if p in PROTOS and allowed(p):
+            return p
+        if rows <= 16:
+            return "ll"
+        return "nvls" if allowed("nvls") else "flag"
 
     # ------------------------------------------------------------------ tensors
     def empty(self, *shape, dtype=torch.bfloat16):
@@ -186,41 +231,81 @@ class Communicator:
     # -------------------------------------------------------------- collectives
     def all_reduce(self, inp: TensorOrList, out: Optional[TensorOrList] = None, algo="auto",
                    blocks: int = 0, threads: int = 0, nnodes: int = 1, routes: int = 0):
+        """algo: a name from ALGOS, the reference's ids 0-3, or "auto" (the measured table)."""
         ins = self._as_list(inp)
         outs = self._as_list(out) if out is not None else [torch.empty_like(x) for x in ins]
+        if algo == "auto" and os.environ.get("PENNY_ALGO"):
+            algo = os.environ["PENNY_ALGO"]
         ops.comm_all_reduce(self._h, ins, outs, _algo_id(algo), blocks, threads, nnodes, routes,
                             self.is_symmetric(ins), self.is_symmetric(outs))
         return self._ret(outs)
 
-    def reduce_scatter(self, inp: TensorOrList, out: Optional[TensorOrList] = None, nvls: bool = False,
-                       blocks: int = 0, threads: int = 0, pipelined: bool = False):
-        """out[numel / world] = this rank's shard of the sum.  pipelined=True: the push
-        variant that reduces one chunk while the next is on the wire (large shards)."""
+    def reduce_scatter(self, inp: TensorOrList, out: Optional[TensorOrList] = None, nvls: Optional[bool] = None,
+                       blocks: int = 0, threads: int = 0, pipelined: Optional[bool] = None, algo: str = "auto"):
+        """out[numel / world] = this rank's shard of the sum.
+
+        algo: "push" (peers write their slices into the owner's scratch, the owner adds them up),
+        "pipelined" (the same, one chunk reduced while the next is on the wire: large shards),
+        "nvls" (the switch adds; inputs outside the heap are staged) or "auto" (the measured
+        table).  The `nvls=` / `pipelined=` flags of earlier versions still select directly."""
         ins = self._as_list(inp)
         if out is None:
             outs = [torch.empty(x.numel() // self.world_size, dtype=x.dtype, device=x.device) for x in ins]
         else:
             outs = self._as_list(out)
-        ops.comm_reduce_scatter(self._h, ins, outs, nvls, blocks, threads, self.is_symmetric(ins), pipelined)
+        sym = self.is_symmetric(ins)
+        if nvls is not None or pipelined is not None:
+            algo = "nvls" if nvls else ("pipelined" if pipelined else "push")
+        elif algo == "auto":
+            nbytes = ins[0].numel() * ins[0].element_size()
+            algo = self._pick("reduce_scatter", nbytes // self.world_size, ins[0].dtype, sym) or "push"
+        shard_bytes = ins[0].numel() // self.world_size * ins[0].element_size()
+        if algo == "nvls" and (self.emulated or not self.has_multicast or shard_bytes % 16 != 0):
+            algo = "push"
+        if algo not in ("push", "pipelined", "nvls"):
+            raise ValueError(f"unknown reduce-scatter algorithm {algo!r}")
+        ops.comm_reduce_scatter(self._h, ins, outs, algo == "nvls", blocks, threads, sym, algo == "pipelined")
         return self._ret(outs)
 
-    def all_gather(self, inp: TensorOrList, out: Optional[TensorOrList] = None, nvls: bool = False,
-                   blocks: int = 0, threads: int = 0):
+    def all_gather(self, inp: TensorOrList, out: Optional[TensorOrList] = None, nvls: Optional[bool] = None,
+                   blocks: int = 0, threads: int = 0, algo: str = "auto"):
+        """out = concatenation of every rank's `inp`.  algo: "push" (every rank writes its shard into
+        every peer), "nvls" (one multicast store per vector; needs an output from `empty()` and a
+        16-byte-multiple shard) or "auto" (the measured table)."""
         ins = self._as_list(inp)
         if out is None:
             outs = [torch.empty(x.numel() * self.world_size, dtype=x.dtype, device=x.device) for x in ins]
         else:
             outs = self._as_list(out)
-        ops.comm_all_gather(self._h, ins, outs, nvls, blocks, threads, self.is_symmetric(outs))
+        sym = self.is_symmetric(outs)
+        nbytes = ins[0].numel() * ins[0].element_size()
+        if nvls is not None:
+            algo = "nvls" if nvls else "push"
+        elif algo == "auto":
+            algo = self._pick("all_gather", nbytes, ins[0].dtype, sym) or "push"
+            if algo == "nvls" and (self.emulated or not self.has_multicast or not sym or nbytes % 16 != 0):
+                algo = "push"
+        if algo not in ("push", "nvls"):
+            raise ValueError(f"unknown all-gather algorithm {algo!r}")
+        ops.comm_all_gather(self._h, ins, outs, algo == "nvls", blocks, threads, sym)
         return self._ret(outs)
 
     def all_to_all(self, inp: TensorOrList, out: Optional[TensorOrList] = None, blocks: int = 0,
-                   threads: int = 0, pipelined: bool = False):
-        """out[s * n : (s + 1) * n] = rank s's in[rank * n : (rank + 1) * n].  pipelined=True (ordinary
-        output tensors only): one piece is copied out of scratch while the next is on the wire."""
+                   threads: int = 0, pipelined: Optional[bool] = None, algo: str = "auto"):
+        """out[s * n : (s + 1) * n] = rank s's in[rank * n : (rank + 1) * n].  algo: "push", "pipelined"
+        (ordinary output tensors only: one piece is copied out of scratch while the next is on the
+        wire) or "auto" (the measured table)."""
         ins = self._as_list(inp)
         outs = self._as_list(out) if out is not None else [torch.empty_like(x) for x in ins]
-        ops.comm_all_to_all(self._h, ins, outs, blocks, threads, self.is_symmetric(outs), pipelined)
+        sym = self.is_symmetric(outs)
+        if pipelined is not None:
+            algo = "pipelined" if pipelined else "push"
+        elif algo == "auto":
+            nbytes = ins[0].numel() // self.world_size * ins[0].element_size()
+            algo = self._pick("all_to_all", nbytes, ins[0].dtype, sym) or "push"
+        if algo not in ("push", "pipelined"):
+            raise ValueError(f"unknown all-to-all algorithm {algo!r}")
+        ops.comm_all_to_all(self._h, ins, outs, blocks, threads, sym, algo == "pipelined")
         return self._ret(outs)
 
     def exchange(self, buf: TensorOrList, peer: Union[int, Sequence[int]], blocks: int = 0, threads: int = 0):
@@ -236,7 +321,8 @@ class Communicator:
                                  eps: float = 1e-5, proto: str = "ll", blocks: int = 0, threads: int = 0):
         """out = rmsnorm(all_reduce(inp) + residual) * weight; residual_out = all_reduce(inp) + residual.
 
-        proto: "ll" (flag-in-data pushes, a handful of rows), "flag" (pushes + one flag barrier),
+        proto: "auto" (the measured table, restricted to what these tensors allow),
+        "ll" (flag-in-data pushes, a handful of rows), "flag" (pushes + one flag barrier),
         "nvls" (switch reduction, rows sharded over the ranks, result multicast: `inp` and `out`
         must come from `empty()`; each rank keeps the residual of its own rows only) or
         "nvls_oneshot" (every rank pulls all rows switch-reduced: `inp` from `empty()`, and
@@ -244,6 +330,9 @@ class Communicator:
         ins = self._as_list(inp)
         outs = self._as_list(out) if out is not None else [torch.empty_like(x) for x in ins]
         res = self._as_list(residual) if residual is not None else []
+        if proto == "auto":
+            proto = self.pick_fused_proto(ins[0].shape[0], ins[0].shape[1], ins[0].dtype, self.is_symmetric(ins),
+                                          self.is_symmetric(outs))
         if residual_out is not None:
             rout = self._as_list(residual_out)
         else:

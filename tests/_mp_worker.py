@@ -76,6 +76,19 @@ def main():
                     torch.testing.assert_close(xs.float().cpu(), want, **TOL[dtype])
                 check(f"all_reduce/nvls-symmetric/{dtype}/{n}", run_sym)
 
+                def run_oneshot_in_place():
+                    # every rank reads all inputs through the switch while the others may already be
+                    # storing: an output that aliases the symmetric input is served from a staged copy
+                    xs = comm.empty(n, dtype=dtype)
+                    for _ in range(2):
+                        xs.copy_(x)
+                        torch.cuda.synchronize()
+                        dist.barrier()
+                        comm.all_reduce(xs, out=xs, algo="nvls_oneshot")
+                        comm.check()
+                        torch.testing.assert_close(xs.float().cpu(), want, **TOL[dtype])
+                check(f"all_reduce/nvls_oneshot-in-place/{dtype}/{n}", run_oneshot_in_place)
+
             shard = n
             big = (torch.rand(shard * world, device="cuda", generator=g) * 2 - 1).to(dtype)
             bparts = gather_cpu(big)

@@ -163,27 +163,55 @@ def test_gloo_peer_exit_is_detected():
 
 
 def test_tuner_roundtrip(tmp_path):
+    """Sweep records -> table keyed by (op, world, dtype, memory class) -> lookups -> JSON and back,
+    through the class and through the command line."""
     import json
     sys.path.insert(0, ROOT)
-    from penny_b200.parallel.tuner import Tuner
+    from penny_b200.parallel.tuner import Tuner, _main
     rows = []
     for size, times in ((1024, {"oneshot_ll": 5, "oneshot": 7, "nvls": 12}), (1 << 20, {"oneshot_ll": 80, "oneshot": 30, "nvls": 25}),
                         (1 << 26, {"twoshot": 400, "nvls": 250})):
         for algo, t in times.items():
+            rows.append(dict(op="all_reduce", impl="penny", algo=algo, world=8, dtype="bf16", bytes=size, t_us=t, symmetric=True))
+    # ordinary memory: the switch pays staging copies and loses at the top end
+    for size, times in ((1024, {"oneshot_ll": 5, "nvls": 14}), (1 << 26, {"twoshot": 300, "nvls": 330})):
+        for algo, t in times.items():
             rows.append(dict(op="all_reduce", impl="penny", algo=algo, world=8, dtype="bf16", bytes=size, t_us=t))
+    # a graph time wins over the eager time of the same point; "auto" and NCCL rows are ignored
+    rows.append(dict(op="all_reduce", impl="penny", algo="oneshot", world=4, dtype="fp32", bytes=4096, t_us=9, t_graph_us=3))
+    rows.append(dict(op="all_reduce", impl="penny", algo="oneshot_ll", world=4, dtype="fp32", bytes=4096, t_us=5, t_graph_us=4))
+    rows.append(dict(op="all_reduce", impl="penny", algo="auto", world=4, dtype="fp32", bytes=4096, t_us=1))
+    rows.append(dict(op="all_reduce", impl="nccl", world=4, dtype="fp32", bytes=4096, t_us=1))
+    for size, times in ((1 << 12, {"push": 20, "nvls": 25}), (1 << 24, {"push": 300, "pipelined": 250, "nvls": 260})):
+        for algo, t in times.items():
+            rows.append(dict(op="reduce_scatter", impl="penny", algo=algo, world=8, dtype="bf16", bytes=size, t_us=t))
+    for nbytes, times in ((8 * 8192, {"ll": 6, "nvls": 14, "nvls_oneshot": 9}), (64 * 8192, {"ll": 30, "nvls": 16, "nvls_oneshot": 11})):
+        for algo, t in times.items():
+            rows.append(dict(op="fused_norm", impl="penny", algo=algo, world=8, dtype="bf16", bytes=nbytes, t_graph_us=t, symmetric=True))
     p = tmp_path / "sweep.jsonl"
     p.write_text("\n".join(json.dumps(r) for r in rows))
     t = Tuner.from_sweep(str(p))
-    assert t.pick(512, 8) == "oneshot_ll" and t.pick(1 << 19, 8) == "nvls" and t.pick(1 << 30, 8) == "nvls"
-    assert t.pick(1 << 30, 8, has_multicast=False) == "twoshot"
+    ar = lambda n, **kw: t.pick("all_reduce", n, 8, "bf16", **kw)  # noqa: E731
+    assert ar(512, symmetric=True) == "oneshot_ll" and ar(1 << 19, symmetric=True) == "nvls" and ar(1 << 30, symmetric=True) == "nvls"
+    assert ar(1 << 30) == "twoshot" and ar(512) == "oneshot_ll"            # ordinary memory has its own rows
+    assert ar(1 << 30, symmetric=True, has_multicast=False) is None         # the caller falls back to its rule
+    assert t.pick("all_reduce", 4096, 4, "fp32") == "oneshot"               # graph time decides
+    assert t.pick("all_reduce", 4096, 4, torch.float32) == "oneshot"        # torch dtypes are accepted
+    assert t.pick("all_reduce", 4096, 2, "bf16") is None                    # nothing measured at 2 ranks
+    assert t.pick("reduce_scatter", 1 << 10, 8) == "push" and t.pick("reduce_scatter", 1 << 26, 8) == "pipelined"
+    assert t.pick("fused_norm", 8 * 8192, 8, symmetric=True) == "ll" and t.pick("fused_norm", 64 * 8192, 8, symmetric=True) == "nvls_oneshot"
     saved = t.save(str(tmp_path / "cache.json"))
-    assert Tuner.load(saved).table == {k: [tuple(x) for x in v] for k, v in t.table.items()} or Tuner.load(saved).pick(512, 8) == "oneshot_ll"
-    assert Tuner().pick(4096, 8) == "oneshot_ll"
-    # the command-line form writes the same cache
-    from penny_b200.parallel.tuner import _main
+    again = Tuner.load(saved)
+    assert again.source == saved and again.pick("all_reduce", 1 << 19, 8, "bf16", symmetric=True) == "nvls"
+    assert "all_reduce world 8 bf16 sym" in again.describe()
+    # the package ships a built-in table (or, failing that, fallback rows) for 2, 4 and 8 ranks
+    builtin = Tuner.load(str(tmp_path / "does_not_exist.json"))
+    for world in (2, 4, 8):
+        assert builtin.pick("all_reduce", 4096, world, "bf16") is not None
+    # the command-line form writes the same table
     cli_out = tmp_path / "cli_cache.json"
-    assert _main([str(p), "--out", str(cli_out), "--dtype", "bf16"]) == 0
-    assert Tuner.load(str(cli_out)).pick(1 << 19, 8) == "nvls"
+    assert _main([str(p), "--out", str(cli_out), "--tolerance", "0"]) == 0
+    assert Tuner.load(str(cli_out)).table == json.loads(json.dumps(t.table))
     empty = tmp_path / "empty.jsonl"
     empty.write_text("")
     assert _main([str(empty), "--out", str(tmp_path / "none.json")]) == 1
