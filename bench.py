@@ -45,7 +45,7 @@ def parse():
     p.add_argument("--batch", type=int, default=64)
     p.add_argument("--kv-len", type=int, default=2048)
     p.add_argument("--backend", default="penny", choices=["penny", "penny_unfused", "nccl"])
-    p.add_argument("--proto", default="auto", choices=["auto", "ll", "flag", "nvls", "nvls_oneshot"])
+    p.add_argument("--proto", default="auto", choices=["auto", "ll", "ll_twoshot", "flag", "nvls", "nvls_oneshot"])
     p.add_argument("--linears", default="penny", choices=["penny", "cublas"],
                    help="penny: this library's tcgen05 decode GEMM (default); cublas: torch.matmul, for comparison")
     p.add_argument("--layers", type=int, default=32, help="debug only: anything but 32 is not the named config")

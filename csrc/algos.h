@@ -24,7 +24,6 @@ enum Algo : int {
   OP_EXCHANGE = 19,
   OP_REDUCE_SCATTER_PIPELINED = 20,
   OP_ALL_TO_ALL_PIPELINED = 21,
-  ALGO_TWOSHOT_PIPELINED = 22,
 };
 
 inline const char* algo_name(int a) {
@@ -44,7 +43,6 @@ inline const char* algo_name(int a) {
     case OP_EXCHANGE: return "exchange";
     case OP_REDUCE_SCATTER_PIPELINED: return "reduce_scatter_pipelined";
     case OP_ALL_TO_ALL_PIPELINED: return "all_to_all_pipelined";
-    case ALGO_TWOSHOT_PIPELINED: return "twoshot_pipelined";
     default: return "auto";
   }
 }

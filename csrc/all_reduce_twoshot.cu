@@ -15,14 +15,6 @@ cudaError_t launch_all_reduce_twoshot(int dtype, const CommCtx& c, const CollArg
   return rc;
 }
 
-cudaError_t launch_all_reduce_twoshot_pipelined(int dtype, const CommCtx& c, const CollArgs* a,
-                                                const LaunchCfg& cfg) {
-  cudaError_t rc = cudaErrorInvalidValue;
-  PENNY_DISPATCH_DTYPE(dtype, T, PENNY_DISPATCH_WORLD(c.world, NG, return cudaErrorInvalidValue, {
-    rc = launch_body<TwoShotPipelined<T, NG>, CollArgs>(c, a, cfg);
-  }));
-  return rc;
-}
 
 cudaError_t launch_reduce_scatter(int dtype, const CommCtx& c, const CollArgs* a,
                                   const LaunchCfg& cfg) {

@@ -121,143 +121,6 @@ struct TwoShot {
   }
 };
 
-// Two-shot all-reduce as a three-stage software pipeline.  Every rank's chunk is
-// cut into up to kTsMaxPieces pieces; in iteration k a block
-//   1. waits for the scatter of piece k - 1, reduces it and pushes the result to
-//      every peer (gather), then raises gather step k on CH_DATA,
-//   2. scatters piece k to its owners and raises scatter step k + 1 on CH_BARRIER,
-//   3. waits for gather step k - 1 and copies piece k - 2 from the gather area to
-//      the output (skipped when the peers wrote the output directly),
-// so the stores of stages 1 and 2 drain over NVLink while stage 3 and the next
-// iteration's reduction run from local memory.  The plain TwoShot runs the three
-// stages one after the other over the whole message.  Same scratch layout; the two
-// flag sequences live on different channels, each monotone inside the call.
-constexpr int kTsMaxPieces = 16;
-
-template <typename T, int NG>
-struct TwoShotPipelined {
-  static PK_DEV void body(const CommCtx& c, int rank, const CollArgs& a, const Blk& b, u64 seq,
-                          int& s_abort) {
-    constexpr size_t E = 16 / sizeof(T);
-    const T* in = reinterpret_cast<const T*>(a.in);
-    T* out = reinterpret_cast<T*>(a.out);
-    const size_t V = ceil_div(a.n, E);
-    const size_t CV = ceil_div(V, (size_t)NG);
-    const size_t rs_off = scratch_half(a.scratch_off, a.scratch_bytes, seq);
-    const size_t ag_off = rs_off + (size_t)NG * CV * 16;
-    const bool direct = a.out_heap_off != kNotInHeap;
-    const size_t stride = (size_t)b.nblocks * b.nthreads;
-    const size_t first = (size_t)b.bid * b.nthreads;
-    const size_t per_pass = stride * kBatch;
-    const size_t passes = ceil_div(CV, per_pass);
-    int pieces = (int)(passes / 4);
-    if (pieces < 1) pieces = 1;
-    if (pieces > kTsMaxPieces) pieces = kTsMaxPieces;
-    const size_t PS = ceil_div(passes, (size_t)pieces) * per_pass;  // vectors of a chunk per piece
-    const Span mine = split_span(V, NG, rank);
-    const size_t mine_len = mine.end - mine.begin;
-
-    for (int k = 0; k <= pieces + 1; ++k) {
-      // ---- stage 1: reduce piece k - 1 of my chunk, push it to everyone
-      if (k >= 1 && k <= pieces) {
-        PK_FOR_THREADS(b, _t) {
-          if (_t < c.world && _t != rank) {
-            if (!wait_peer(c, rank, _t, CH_BARRIER, b, flag_value(seq, k), ST_TIMEOUT_BARRIER)) s_abort = 1;
-          }
-        }
-        PK_SYNC(b);
-        if (s_abort) return;
-        const size_t lo = (size_t)(k - 1) * PS, hi = (lo + PS < mine_len) ? lo + PS : mine_len;
-        PK_FOR_THREADS(b, tid) {
-          for (size_t j = lo + first + tid; j < hi; j += stride) {
-            float acc[E];
-#pragma unroll
-            for (size_t i = 0; i < E; ++i) acc[i] = 0.f;
-#pragma unroll
-            for (int s = 0; s < NG; ++s) {
-              V16 x = (s == rank) ? load_user_vec<T>(in, mine.begin + j, a.n)
-                                  : ld16(c.heap[rank] + rs_off + ((size_t)s * CV + j) * 16);
-              unpack_add<T>(x, acc);
-            }
-            const V16 r = pack<T>(acc);
-            const size_t v = mine.begin + j;
-            store_user_vec<T>(out, v, a.n, r);
-#pragma unroll
-            for (int d = 1; d < NG; ++d) {
-              const int p = (rank + d) % NG;
-              if (direct)
-                store_user_vec<T>(reinterpret_cast<T*>(c.heap[p] + a.out_heap_off), v, a.n, r);
-              else
-                st16(c.heap[p] + ag_off + v * 16, r);
-            }
-          }
-        }
-        PK_SYNC(b);
-        PK_FOR_THREADS(b, _t) {
-          if (_t < c.world && _t != rank) signal_peer(c, rank, _t, CH_DATA, b, flag_value(seq, k));
-        }
-      }
-      // ---- stage 2: scatter piece k of every peer's chunk
-      if (k < pieces) {
-        PK_FOR_THREADS(b, tid) {
-          for (int d = 1; d < NG; ++d) {
-            const int dst = (rank + d) % NG;
-            const Span sp = split_span(V, NG, dst);
-            const size_t len = sp.end - sp.begin;
-            const size_t lo = (size_t)k * PS, hi = (lo + PS < len) ? lo + PS : len;
-            for (size_t j0 = lo + first + tid; j0 < hi; j0 += kBatch * stride) {
-              V16 x[kBatch];
-#pragma unroll
-              for (int u = 0; u < kBatch; ++u)
-                if (j0 + u * stride < hi) x[u] = load_user_vec<T>(in, sp.begin + j0 + u * stride, a.n);
-#pragma unroll
-              for (int u = 0; u < kBatch; ++u)
-                if (j0 + u * stride < hi)
-                  st16(c.heap[dst] + rs_off + ((size_t)rank * CV + j0 + u * stride) * 16, x[u]);
-            }
-          }
-        }
-        PK_SYNC(b);
-        PK_FOR_THREADS(b, _t) {
-          if (_t < c.world && _t != rank) signal_peer(c, rank, _t, CH_BARRIER, b, flag_value(seq, k + 1));
-        }
-      }
-      // ---- stage 3: piece k - 2 of every peer's result has arrived: copy it out
-      if (k >= 2) {
-        PK_FOR_THREADS(b, _t) {
-          if (_t < c.world && _t != rank) {
-            if (!wait_peer(c, rank, _t, CH_DATA, b, flag_value(seq, k - 1), ST_TIMEOUT_DATA)) s_abort = 1;
-          }
-        }
-        PK_SYNC(b);
-        if (s_abort) return;
-        if (!direct) {
-          PK_FOR_THREADS(b, tid) {
-            for (int d = 1; d < NG; ++d) {
-              const int src = (rank + d) % NG;
-              const Span sp = split_span(V, NG, src);
-              const size_t len = sp.end - sp.begin;
-              const size_t lo = (size_t)(k - 2) * PS, hi = (lo + PS < len) ? lo + PS : len;
-              for (size_t j0 = lo + first + tid; j0 < hi; j0 += kBatch * stride) {
-                V16 x[kBatch];
-#pragma unroll
-                for (int u = 0; u < kBatch; ++u)
-                  if (j0 + u * stride < hi) x[u] = ld16(c.heap[rank] + ag_off + (sp.begin + j0 + u * stride) * 16);
-#pragma unroll
-                for (int u = 0; u < kBatch; ++u)
-                  if (j0 + u * stride < hi) store_user_vec<T>(out, sp.begin + j0 + u * stride, a.n, x[u]);
-              }
-            }
-          }
-        }
-      }
-    }
-  }
-  static PK_DEV void run(const CommCtx& c, int rank, const CollArgs& a, const Blk& b) {
-    run_collective<TwoShotPipelined<T, NG>, CollArgs>(c, rank, a, b);
-  }
-};
-
 // Reduce-scatter.  The input has a.n elements and is cut into `world` equal
 // shards of a.n / world elements (a.n must divide); rank r receives the sum of
 // shard r.  Shard order = rank order, as in the reference's

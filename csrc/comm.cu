@@ -263,12 +263,6 @@ void Communicator::run_all_reduce_once(int algo, int dtype, const void* const* i
       rc = launch_all_reduce_twoshot(dtype, ctx_, a, cfg_for(ceil_div(V, world_), t, stream, 128, 1));
       break;
     }
-    case ALGO_TWOSHOT_PIPELINED: {
-      // always through the gather area (the variant the host simulator has proven)
-      set_scratch(ensure(scratch_, twoshot_scratch_bytes(n, es, world_), "two-shot"));
-      rc = launch_all_reduce_twoshot_pipelined(dtype, ctx_, a, cfg_for(ceil_div(V, world_), t, stream, 128, 1));
-      break;
-    }
     case ALGO_RING_SIMPLE: {
       set_scratch(ensure(scratch_, ring_simple_scratch_bytes(n, es, world_), "ring"));
       rc = launch_all_reduce_ring_simple(dtype, ctx_, a, cfg_for(V, t, stream, 64, 1));
@@ -540,7 +534,7 @@ void Communicator::fused_ar_rmsnorm(int dtype, int proto, const void* const* in,
       throw std::runtime_error("penny: NVLS fused norm needs symmetric heap tensors for in and out");
     cfg.blocks = t.blocks > 0 ? t.blocks : std::min(max_blocks, std::max(1, (rows + world_ - 1) / world_));
   } else {
-    Region& r = ensure(proto == FUSED_PROTO_LL ? scratch_ll_ : scratch_,
+    Region& r = ensure(proto == FUSED_PROTO_LL || proto == FUSED_PROTO_LL_TWOSHOT ? scratch_ll_ : scratch_,
                        fused_norm_scratch_bytes(proto, rows, hidden, es, world_), "fused norm");
     for (int v = 0; v < nv; ++v) {
       a[v].scratch_off = r.off;

@@ -19,6 +19,8 @@
 //         keeps the residual of the rows it owns.  Least wire traffic.
 //   NVLS one-shot  every rank pulls all rows switch-reduced and normalises them
 //         itself: half the latency steps, `world` times the wire bytes.
+//   LL two-shot  rows sharded over the ranks, flag-in-data lines to the owner and
+//         back: two one-way trips, no barrier, 1 / world of the one-shot bytes.
 // Plus the communication-free kernel (add_rmsnorm) used at world size 1.
 //
 // The reference stops at the plain all-reduce (penny/custom_all_reduce.py:229-267);
@@ -240,6 +242,138 @@ __device__ __forceinline__ void mm_st(void* p, const V16& v) {
                : "memory");
 }
 
+// ---------------------------------------------------------------------------
+// Two-shot with flag-in-data lines in BOTH directions: rows are sharded over the
+// ranks; every rank pushes its partial of a row to the row's owner as LL lines,
+// the owner adds them in rank order, adds the residual, normalises and sends the
+// finished row to every rank, again as LL lines (one multicast store per line
+// when the heap is bound to the switch, else one store per peer).  No flag
+// barrier and no fence anywhere: the critical path is two one-way trips, and a
+// rank moves rows * hidden / world elements per direction instead of rows *
+// hidden.  One block handles one row from end to end (its owner's block reduces,
+// every other rank's block pushes and then polls for the result), so blocks never
+// wait for one another.  The residual stream stays sharded like under NVLS.
+// scratch half: [world src][rows per rank][HV] line pairs, then [rows][HV] line pairs
+// ---------------------------------------------------------------------------
+template <typename T, int NG>
+struct FusedTwoShotLLNorm {
+  static __device__ void body(const CommCtx& c, int rank, const FusedNormArgs& a, const Blk& b,
+                              u64 seq, int& s_abort) {
+    constexpr int E = 16 / sizeof(T);
+    __shared__ float smem[32];
+    const int HV = a.hidden / E;
+    const int per = (a.rows + NG - 1) / NG;  // rows per rank, as split_span deals them out
+    const size_t base = scratch_half(a.scratch_off, a.scratch_bytes, seq);
+    const size_t p2 = base + (size_t)NG * per * HV * 32;
+    const uint32_t e = ll_flag(seq);
+    const T* in = reinterpret_cast<const T*>(a.in);
+    const T* w = reinterpret_cast<const T*>(a.weight);
+    (void)s_abort;
+    auto to_lines = [&](const V16& x, V16& l0, V16& l1) {
+      l0.w[0] = x.w[0]; l0.w[1] = e; l0.w[2] = x.w[1]; l0.w[3] = e;
+      l1.w[0] = x.w[2]; l1.w[1] = e; l1.w[2] = x.w[3]; l1.w[3] = e;
+    };
+    for (size_t row = b.bid; row < (size_t)a.rows; row += b.nblocks) {
+      const int owner = (int)(row / per), lrow = (int)(row % per);
+      bool ok = true;
+      if (owner != rank) {
+        // my partial of the row -> its owner
+        for (int v = threadIdx.x; v < HV; v += blockDim.x) {
+          V16 l0, l1;
+          to_lines(ld16(in + row * a.hidden + (size_t)v * E), l0, l1);
+          char* dst = c.heap[owner] + base + (((size_t)rank * per + lrow) * HV + v) * 32;
+          st16_volatile(dst, l0);
+          st16_volatile(dst + 16, l1);
+        }
+        // the finished row comes back the same way
+        T* out = reinterpret_cast<T*>(a.out) + row * (size_t)a.hidden;
+        for (int v = threadIdx.x; v < HV && ok; v += blockDim.x) {
+          const char* src = c.heap[rank] + p2 + ((size_t)row * HV + v) * 32;
+          V16 l0, l1, x;
+          ok = ll_wait_line(src, e, l0, c, owner, b.bid) && ll_wait_line(src + 16, e, l1, c, owner, b.bid);
+          x.w[0] = l0.w[0]; x.w[1] = l0.w[2]; x.w[2] = l1.w[0]; x.w[3] = l1.w[2];
+          if (ok) st16(out + (size_t)v * E, x);
+        }
+        if (__syncthreads_or(ok ? 0 : 1)) return;
+        continue;
+      }
+      // owner: the world's partials in rank order + residual
+      float z[kMaxVecPerThread][E];
+      int nv = 0;
+#pragma unroll
+      for (int k = 0; k < kMaxVecPerThread; ++k) {
+        const int v = threadIdx.x + k * blockDim.x;
+        if (v < HV) {
+          nv = k + 1;
+#pragma unroll
+          for (int i = 0; i < E; ++i) z[k][i] = 0.f;
+#pragma unroll
+          for (int s = 0; s < NG; ++s) {
+            V16 x;
+            if (s == rank) {
+              x = ld16(in + row * a.hidden + (size_t)v * E);
+            } else {
+              const char* src = c.heap[rank] + base + (((size_t)s * per + lrow) * HV + v) * 32;
+              V16 l0, l1;
+              ok = ok && ll_wait_line(src, e, l0, c, s, b.bid);
+              ok = ok && ll_wait_line(src + 16, e, l1, c, s, b.bid);
+              x.w[0] = l0.w[0]; x.w[1] = l0.w[2]; x.w[2] = l1.w[0]; x.w[3] = l1.w[2];
+            }
+            unpack_add<T>(x, z[k]);
+          }
+          if (a.residual)
+            unpack_add<T>(ld16(reinterpret_cast<const T*>(a.residual) + row * a.hidden + (size_t)v * E), z[k]);
+        }
+      }
+      if (__syncthreads_or(ok ? 0 : 1)) return;
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < kMaxVecPerThread; ++k) {
+        if (k < nv) {
+#pragma unroll
+          for (int i = 0; i < E; ++i) ss += z[k][i] * z[k][i];
+        }
+      }
+      ss = block_sum(ss, smem);
+      const float rstd = rsqrtf(ss / (float)a.hidden + a.eps);
+      T* out = reinterpret_cast<T*>(a.out) + row * (size_t)a.hidden;
+      T* rout = a.residual_out ? reinterpret_cast<T*>(a.residual_out) + row * (size_t)a.hidden : nullptr;
+#pragma unroll
+      for (int k = 0; k < kMaxVecPerThread; ++k) {
+        if (k < nv) {
+          const int v = threadIdx.x + k * blockDim.x;
+          if (rout) st16(rout + (size_t)v * E, pack<T>(z[k]));
+          float wf[E], o[E];
+          unpack_set<T>(ld16(w + (size_t)v * E), wf);
+#pragma unroll
+          for (int i = 0; i < E; ++i) o[i] = z[k][i] * rstd * wf[i];
+          const V16 xo = pack<T>(o);
+          st16(out + (size_t)v * E, xo);
+          V16 l0, l1;
+          to_lines(xo, l0, l1);
+          const size_t off = p2 + ((size_t)row * HV + v) * 32;
+#if !defined(PENNY_HOST_SIM)
+          if (c.mc != nullptr) {
+            mm_st(c.mc + off, l0);  // one store, every rank's copy
+            mm_st(c.mc + off + 16, l1);
+            continue;
+          }
+#endif
+#pragma unroll
+          for (int d = 1; d < NG; ++d) {
+            char* dst = c.heap[(rank + d) % NG] + off;
+            st16_volatile(dst, l0);
+            st16_volatile(dst + 16, l1);
+          }
+        }
+      }
+    }
+  }
+  static __device__ void run(const CommCtx& c, int rank, const FusedNormArgs& a, const Blk& b) {
+    run_collective<FusedTwoShotLLNorm<T, NG>, FusedNormArgs>(c, rank, a, b);
+  }
+};
+
 // Two transports through the switch:
 //   two-shot  rows are sharded over the ranks; the owner pulls the switch-reduced
 //             row, normalises it and multicasts the result (multimem.st) into every
@@ -365,6 +499,12 @@ cudaError_t launch_fused_ar_rmsnorm(int dtype, int proto, const CommCtx& c, cons
                    : launch_kernel_ex(k_fused_nvls_norm<T, false>, dim3(cfg.blocks), dim3(cfg.threads), 0, cfg.stream,
                                       true, 1, c, a[0]);
     });
+    return rc;
+  }
+  if (proto == FUSED_PROTO_LL_TWOSHOT) {
+    PENNY_DISPATCH_DTYPE(dtype, T, PENNY_DISPATCH_WORLD(c.world, NG, return cudaErrorInvalidValue, {
+      rc = launch_body<FusedTwoShotLLNorm<T, NG>, FusedNormArgs>(c, a, cfg);
+    }));
     return rc;
   }
   PENNY_DISPATCH_DTYPE(dtype, T, PENNY_DISPATCH_WORLD(c.world, NG, return cudaErrorInvalidValue, {

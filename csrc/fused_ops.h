@@ -8,7 +8,13 @@ namespace penny {
 
 struct LaunchCfg;
 
-enum FusedProto : int { FUSED_PROTO_LL = 0, FUSED_PROTO_FLAG = 1, FUSED_PROTO_NVLS = 2, FUSED_PROTO_NVLS_ONESHOT = 3 };
+enum FusedProto : int {
+  FUSED_PROTO_LL = 0,
+  FUSED_PROTO_FLAG = 1,
+  FUSED_PROTO_NVLS = 2,
+  FUSED_PROTO_NVLS_ONESHOT = 3,
+  FUSED_PROTO_LL_TWOSHOT = 4,
+};
 
 // all-reduce + residual add + RMSNorm over [rows, hidden]
 struct FusedNormArgs {
@@ -28,7 +34,13 @@ struct FusedNormArgs {
 
 // scratch for the one-shot protocols (both halves)
 inline size_t fused_norm_scratch_bytes(int proto, int rows, int hidden, int elem_size, int world) {
-  size_t v = (size_t)rows * (size_t)(hidden * elem_size / 16);
+  const size_t hv = (size_t)(hidden * elem_size / 16);
+  if (proto == FUSED_PROTO_LL_TWOSHOT) {
+    // per half: line pairs of [world][rows per rank][hv] partials and of [rows][hv] finished rows
+    const size_t per = (size_t)(rows + world - 1) / world;
+    return 2 * ((size_t)world * per + (size_t)rows) * hv * 32;
+  }
+  size_t v = (size_t)rows * hv;
   return (proto == FUSED_PROTO_LL ? 4 : 2) * (size_t)world * v * 16;
 }
 

@@ -71,8 +71,6 @@ cudaError_t launch_all_reduce_oneshot(int dtype, bool ll, const CommCtx& c, cons
                                       const LaunchCfg& cfg);
 cudaError_t launch_all_reduce_twoshot(int dtype, const CommCtx& c, const CollArgs* a,
                                       const LaunchCfg& cfg);
-cudaError_t launch_all_reduce_twoshot_pipelined(int dtype, const CommCtx& c, const CollArgs* a,
-                                                const LaunchCfg& cfg);
 cudaError_t launch_reduce_scatter(int dtype, const CommCtx& c, const CollArgs* a,
                                   const LaunchCfg& cfg);
 cudaError_t launch_reduce_scatter_pipelined(int dtype, const CommCtx& c, const CollArgs* a,

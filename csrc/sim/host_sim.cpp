@@ -102,7 +102,6 @@ void run_body(int algo, int world, const CommCtx& c, int rank, const CollArgs& a
       case ALGO_ONESHOT: OneShotFlag<T, NG>::run(c, rank, a, b); break;
       case ALGO_ONESHOT_LL: OneShotLL<T, NG>::run(c, rank, a, b); break;
       case ALGO_TWOSHOT: TwoShot<T, NG>::run(c, rank, a, b); break;
-      case ALGO_TWOSHOT_PIPELINED: TwoShotPipelined<T, NG>::run(c, rank, a, b); break;
       case OP_REDUCE_SCATTER: ReduceScatterPush<T, NG>::run(c, rank, a, b); break;
       case OP_REDUCE_SCATTER_PIPELINED: ReduceScatterPipelined<T, NG>::run(c, rank, a, b); break;
       case OP_ALL_GATHER: AllGatherPush<T, NG>::run(c, rank, a, b); break;
@@ -119,8 +118,7 @@ size_t scratch_need(int algo, size_t n, int es, int world, int nnodes, int nbloc
     case ALGO_RING_SIMPLE: return ring_simple_scratch_bytes(n, es, world);
     case ALGO_ONESHOT: return oneshot_flag_scratch_bytes(n, es, world);
     case ALGO_ONESHOT_LL: return oneshot_ll_scratch_bytes(n, es, world);
-    case ALGO_TWOSHOT:
-    case ALGO_TWOSHOT_PIPELINED: return twoshot_scratch_bytes(n, es, world);
+    case ALGO_TWOSHOT: return twoshot_scratch_bytes(n, es, world);
     case ALGO_DOUBLE_RING: return double_ring_scratch_bytes(n, es, world, nnodes, nblocks);
     case ALGO_TREE: return tree_scratch_bytes(n, es, nnodes);
     case OP_REDUCE_SCATTER:

@@ -539,7 +539,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.attr("ALGO_RING_SIMPLE") = (int)ALGO_RING_SIMPLE;
   m.attr("ALGO_ONESHOT") = (int)ALGO_ONESHOT;
   m.attr("ALGO_TWOSHOT") = (int)ALGO_TWOSHOT;
-  m.attr("ALGO_TWOSHOT_PIPELINED") = (int)ALGO_TWOSHOT_PIPELINED;
   m.attr("ALGO_DOUBLE_RING") = (int)ALGO_DOUBLE_RING;
   m.attr("ALGO_TREE") = (int)ALGO_TREE;
   m.attr("ALGO_NVLS") = (int)ALGO_NVLS;
@@ -550,6 +549,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.attr("PROTO_FLAG") = (int)FUSED_PROTO_FLAG;
   m.attr("PROTO_NVLS") = (int)FUSED_PROTO_NVLS;
   m.attr("PROTO_NVLS_ONESHOT") = (int)FUSED_PROTO_NVLS_ONESHOT;
+  m.attr("PROTO_LL_TWOSHOT") = (int)FUSED_PROTO_LL_TWOSHOT;
 
   bind_custom_all_reduce(m);
   bind_gemm(m);

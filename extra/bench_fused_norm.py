@@ -56,7 +56,7 @@ def main(argv=None, ctx=None):
             t_nccl = bench_graph(nccl_pair, inner=5, warmup=5, iters=30)["median_us"] / 2
             rec.add(op="fused_norm", impl="nccl", algo="all_reduce + add_rmsnorm", world=world, dtype="bf16",
                     rows=rows, hidden=H, bytes=nbytes, t_graph_us=round(t_nccl, 2))
-        protos = ["ll", "flag"] + (["nvls", "nvls_oneshot"] if comm.has_multicast else []) + ["auto"]
+        protos = ["ll", "ll_twoshot", "flag"] + (["nvls", "nvls_oneshot"] if comm.has_multicast else []) + ["auto"]
         for proto in protos:
             if proto == "ll" and rows > 128:
                 continue

@@ -132,21 +132,27 @@ def main():
             x = (torch.rand(n, device="cuda", generator=g) * 2 - 1).bfloat16()
             ref = x.clone()
             dist.all_reduce(ref)
+            rs_out = torch.empty(max(1, n // world), device="cuda", dtype=x.dtype)
             for op, call, check in (
                     ("all_reduce", lambda: car.custom_all_reduce(x),
                      lambda o: torch.allclose(o.float(), ref.float(), atol=1e-1, rtol=1e-2)),
-                    # this rank's shard of the sum, at the front of the output or at the shard's own position
-                    ("reduce_scatter", lambda: car.custom_reduce_scatter(x),
-                     lambda o: any(torch.allclose(o[a:a + n // world].float(),
-                                                  ref[rank * (n // world):(rank + 1) * (n // world)].float(),
-                                                  atol=1e-1, rtol=1e-2) for a in (0, rank * (n // world)))),
+                    # the reference's kernel wants an output of exactly one shard (csrc/custom_all_reduce.cu:121;
+                    # its Python default, empty_like(input), fails that check)
+                    ("reduce_scatter", lambda: car.custom_reduce_scatter(x, out=rs_out),
+                     lambda o: torch.allclose(o.float(), ref[rank * (n // world):(rank + 1) * (n // world)].float(),
+                                              atol=1e-1, rtol=1e-2)),
                     ("all_gather", lambda: car.custom_all_gather(x), lambda o: True)):
                 if op == "all_gather" and nbytes * world >= car.max_size:
                     continue
                 if op == "reduce_scatter" and (n % world or (n // world * 2) % 16):
                     continue
                 with Watchdog(args.watchdog_s, rank, f"CustomAllreduce.{op} @ {nbytes} B"):
-                    o = call()
+                    try:
+                        o = call()
+                    except RuntimeError as e:  # e.g. "requires a minimum size of 2048" (csrc/custom_all_reduce.cuh:891-893)
+                        emit(op=op, algo="custom_all_reduce", dtype="bf16", bytes=nbytes,
+                             unsupported=str(e).strip().splitlines()[-1][:120])
+                        continue
                     torch.cuda.synchronize()
                     if o is None:
                         emit(op=op, algo="custom_all_reduce", dtype="bf16", bytes=nbytes, declined=True)

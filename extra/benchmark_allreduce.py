@@ -63,8 +63,7 @@ def main(argv=None, ctx=None):
     names = []
     for a in args.algo:
         if a == "all":
-            names += ["oneshot_ll", "oneshot", "twoshot", "twoshot_pipelined", "ring_simple", "ring_standard",
-                      "double_ring", "tree"]
+            names += ["oneshot_ll", "oneshot", "twoshot", "ring_simple", "ring_standard", "double_ring", "tree"]
             if comm.has_multicast:
                 names += ["nvls_oneshot", "nvls"]
             names += ["auto"]
@@ -131,8 +130,6 @@ def main(argv=None, ctx=None):
                 continue
             if name in ("ring_simple", "tree", "double_ring") and nbytes > (args.max_slow_mib << 20):
                 continue
-            if name == "twoshot_pipelined" and nbytes < (1 << 20):
-                continue  # a pipeline over pieces of a chunk: nothing to overlap below that
             nnodes = args.nnodes if name in ("double_ring", "tree", "ring_standard") else 1
             if name in ("double_ring", "tree") and nnodes == 1 and world >= 4:
                 nnodes = 2

@@ -34,7 +34,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", required=True)
     ap.add_argument("--quick", action="store_true")
-    ap.add_argument("--heap-gib", type=float, default=14.0)
+    ap.add_argument("--heap-gib", type=float, default=40.0)
     ap.add_argument("--skip", nargs="*", default=[], help="parts to leave out: ar ar_sym rs ag a2a fused")
     args = ap.parse_args()
     rank, world, comm = initialize_distributed(heap_bytes=int(args.heap_gib * (1 << 30)))

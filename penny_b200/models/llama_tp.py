@@ -121,7 +121,7 @@ class LlamaTPDecoder:
         self.next_tokens = torch.zeros(B, dtype=torch.int64, device=self.dev)
         self.kcache = [torch.zeros(B, self.Hkv, max_len, D, dtype=dt, device=self.dev) for _ in range(cfg.layers)]
         self.vcache = [torch.zeros(B, self.Hkv, max_len, D, dtype=dt, device=self.dev) for _ in range(cfg.layers)]
-        self.splits = max(1, min(16, -(-2 * 148 // (B * self.Hkv))))
+        self.splits = self.attention_splits(B * self.Hkv, max_len)
         # split partials + self-resetting arrival counters (zero before the first use)
         self.workspace = torch.zeros(ops.decode_attn_fused_workspace_bytes(B, self.Hq, self.Hkv, self.splits),
                                      dtype=torch.uint8, device=self.dev)
@@ -202,6 +202,21 @@ class LlamaTPDecoder:
         F2, H = wgu.shape
         v = wgu.view(F2 // 128, 2, 64, H)
         return v[:, 0].reshape(F2 // 2, H), v[:, 1].reshape(F2 // 2, H)
+
+    @staticmethod
+    def attention_splits(items: int, kv_len: int = 2048, slots: int = 2 * 148, max_splits: int = 16) -> int:
+        """KV splits of the decode attention for `items` = batch x KV heads (row, head) pairs.  Two
+        CTAs fit an SM, so `slots` run at once and a grid a little larger than that costs a whole
+        second wave.  Measured on B200 (TP 8: 320 CTAs took twice as long as 256; TP 1: 2048 short
+        CTAs lost 10 % to 512 long ones): a CTA costs its KV positions plus about 200 positions of
+        fixed work, a launch costs that times its waves; ties go to fewer splits."""
+        best, best_cost = 1, None
+        for s in range(1, max_splits + 1):
+            waves = -(-items * s // slots)
+            cost = waves * (kv_len / s + 200.0)
+            if best_cost is None or cost < best_cost * 0.98:
+                best, best_cost = s, cost
+        return best
 
     def weight_bytes(self) -> int:
         n = self.embed.numel() + self.lm_head.numel()

@@ -34,7 +34,6 @@ ALGOS = {
     "ring_simple": ops.ALGO_RING_SIMPLE,
     "oneshot": ops.ALGO_ONESHOT,
     "twoshot": ops.ALGO_TWOSHOT,
-    "twoshot_pipelined": ops.ALGO_TWOSHOT_PIPELINED,   # three-stage pipeline; not yet timed on hardware
     "double_ring": ops.ALGO_DOUBLE_RING,
     "tree": ops.ALGO_TREE,
     "nvls": ops.ALGO_NVLS,
@@ -42,7 +41,8 @@ ALGOS = {
     "nvls_oneshot": ops.ALGO_NVLS_ONESHOT,
 }
 ALGO_NAMES = {v: k for k, v in ALGOS.items() if k not in ("ring",)}
-PROTOS = {"ll": ops.PROTO_LL, "flag": ops.PROTO_FLAG, "nvls": ops.PROTO_NVLS, "nvls_oneshot": ops.PROTO_NVLS_ONESHOT}
+PROTOS = {"ll": ops.PROTO_LL, "flag": ops.PROTO_FLAG, "nvls": ops.PROTO_NVLS, "nvls_oneshot": ops.PROTO_NVLS_ONESHOT,
+          "ll_twoshot": ops.PROTO_LL_TWOSHOT}
 
 STATUS_NAMES = {
     0: "ok", 1: "timeout in a barrier", 2: "timeout waiting for data", 3: "timeout waiting for a credit",
@@ -192,7 +192,7 @@ class Communicator:
         mc = self.has_multicast and not self.emulated
 
         def allowed(p):
-            return p in ("ll", "flag") or (mc and symmetric_in and (symmetric_out or p == "nvls_oneshot"))
+            return p in ("ll", "flag", "ll_twoshot") or (mc and symmetric_in and (symmetric_out or p == "nvls_oneshot"))
         p = self._pick("fused_norm", nbytes, dtype, symmetric_in)
         if p in PROTOS and allowed(p):
             return p
@@ -322,7 +322,8 @@ class Communicator:
         """out = rmsnorm(all_reduce(inp) + residual) * weight; residual_out = all_reduce(inp) + residual.
 
         proto: "auto" (the measured table, restricted to what these tensors allow),
-        "ll" (flag-in-data pushes, a handful of rows), "flag" (pushes + one flag barrier),
+        "ll" (flag-in-data pushes, a handful of rows), "ll_twoshot" (rows sharded over the ranks,
+        flag-in-data lines to the owner and back; the residual stays sharded), "flag" (pushes + one flag barrier),
         "nvls" (switch reduction, rows sharded over the ranks, result multicast: `inp` and `out`
         must come from `empty()`; each rank keeps the residual of its own rows only) or
         "nvls_oneshot" (every rank pulls all rows switch-reduced: `inp` from `empty()`, and

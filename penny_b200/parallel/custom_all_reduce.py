@@ -8,8 +8,17 @@ static ``create_shared_buffer / free_shared_buffer``.  What differs:
 
 * no NVSHMEM bootstrap (``nvshmem_registered`` / ``symm_mem_enabled`` are
   accepted and ignored) and ``NNODES`` is optional (default 1: one box);
-* the kernels are this library's pull kernels with bounded waits
-  (csrc/custom_all_reduce.cu), sized for B200;
+* on one box the three collectives run on the symmetric-heap communicator's
+  kernels, chosen per message size from the measured table: flag-in-data
+  pushes for the smallest messages, the switch reduction (NVLS) or pushes
+  above.  Those kernels read their input where it is - the owner pushes, or
+  the host stages it into the heap - so nothing has to be registered, in eager
+  mode or under ``capture()``, and the eager path needs no staging copy;
+* the pull kernels with bounded waits (csrc/custom_all_reduce.cu), which read
+  the peers' IPC-registered buffers like the reference's, remain: they serve
+  ``all_reduce(..., registered=True)`` on buffers registered through raw IPC
+  pointers, multi-node groups, and everything when
+  ``PENNY_CUSTOM_AR_BACKEND=pull``;
 * P2P capability is really checked (the reference's ``_can_p2p`` returns True
   unconditionally, :23-30);
 * ``fused_all_reduce_rmsnorm`` – all-reduce + residual add + RMSNorm in one
@@ -63,6 +72,7 @@ class CustomAllreduce:
         self.disabled = True
         self._ptr = 0
         self._comm = None
+        self._own_comm = False
         if not custom_ar or not torch.cuda.is_available():
             logger.info("Custom allreduce is disabled because of missing custom allreduce library or GPU")
             return
@@ -98,6 +108,16 @@ class CustomAllreduce:
         self.fully_connected = True
         self._ptr = ops.init_custom_ar(self.meta_ptrs, self.rank_data, self.rank, self.fully_connected)
         ops.register_buffer(self._ptr, self.buffer_ptrs)
+        # the fast path: a symmetric-heap communicator over the same ranks (one box only)
+        if nnodes == 1 and os.environ.get("PENNY_CUSTOM_AR_BACKEND", "fast") != "pull":
+            try:
+                from .comm import Communicator
+                heap = max(256 << 20, 24 * int(max_size))
+                self._comm = Communicator.create(group, heap_bytes=heap)
+                self._own_comm = True
+            except Exception as e:  # noqa: BLE001
+                logger.warning("CustomAllreduce: no symmetric-heap communicator (%s); using the pull kernels", e)
+                self._comm = None
 
     # ----------------------------------------------------------- graph capture
     @contextmanager
@@ -153,9 +173,18 @@ class CustomAllreduce:
             fn(self._ptr, inp, out, self.buffer_ptrs[self.rank], self.max_size)
         return out
 
-    def _dispatch(self, eager, input, out, warmup_result):
+    @property
+    def fast(self) -> bool:
+        """True when the collectives run on the symmetric-heap communicator's kernels."""
+        return self._comm is not None and not self.disabled
+
+    def _dispatch(self, fast, eager, input, out, warmup_result):
         if self.disabled or not self.should_custom_ar(input):
             return None
+        if self.fast:
+            # nothing to register and nothing to stage: the same call in eager mode, while
+            # warming up for a capture and inside the capture
+            return fast(input, out)
         if self._IS_CAPTURING:
             if torch.cuda.is_current_stream_capturing():
                 return eager(input, out=out, registered=True)
@@ -164,29 +193,52 @@ class CustomAllreduce:
         return eager(input, out=out, registered=False)
 
     def all_reduce(self, inp: torch.Tensor, *, out: torch.Tensor = None, registered: bool = False):
-        """Out-of-place all-reduce.  registered=False copies the input into the
-        pre-registered staging buffer first."""
+        """Out-of-place all-reduce on the pull kernels.  registered=False copies the input into
+        the pre-registered staging buffer first; registered=True reads `inp` through the IPC
+        registration made by register_buffer / register_graph_buffers."""
         if out is None:
             out = torch.empty_like(inp)
         return self._run(ops.all_reduce, inp, out, registered)
 
+    def _fast_all_reduce(self, inp, out):
+        if out is None:
+            out = torch.empty_like(inp)
+        self._comm.all_reduce(inp.view(-1), out=out.view(-1), algo="auto")
+        return out
+
     def custom_all_reduce(self, input: torch.Tensor, out=None) -> Optional[torch.Tensor]:
         """All-reduce with CUDA-graph support; None means "use your fallback"."""
-        return self._dispatch(self.all_reduce, input, out, lambda: torch.empty_like(input))
+        return self._dispatch(self._fast_all_reduce, self.all_reduce, input, out, lambda: torch.empty_like(input))
 
     def reduce_scatter(self, inp: torch.Tensor, *, out: torch.Tensor = None, registered: bool = False):
-        """Out-of-place reduce-scatter; the shard lands in out[: numel // world]."""
+        """Out-of-place reduce-scatter on the pull kernels; the shard lands in out[: numel // world]."""
         if out is None:
             out = torch.empty_like(inp)
         return self._run(ops.reduce_scatter, inp, out, registered)
 
+    def _fast_reduce_scatter(self, inp, out):
+        if out is None:
+            out = torch.empty_like(inp)
+        shard = inp.numel() // self.world_size
+        self._comm.reduce_scatter(inp.view(-1), out=out.view(-1)[:shard], algo="auto")
+        return out
+
     def custom_reduce_scatter(self, input: torch.Tensor, out=None) -> Optional[torch.Tensor]:
-        return self._dispatch(self.reduce_scatter, input, out, lambda: torch.empty_like(input))
+        if not self.disabled and input.numel() % self.world_size != 0:
+            return None
+        return self._dispatch(self._fast_reduce_scatter, self.reduce_scatter, input, out,
+                              lambda: torch.empty_like(input))
 
     def all_gather(self, inp: torch.Tensor, *, out: torch.Tensor = None, registered: bool = False):
         if out is None:
             out = torch.empty(inp.numel() * self.world_size, dtype=inp.dtype, device=inp.device)
         return self._run(ops.all_gather, inp, out, registered)
+
+    def _fast_all_gather(self, inp, out):
+        if out is None:
+            out = torch.empty(inp.numel() * self.world_size, dtype=inp.dtype, device=inp.device)
+        self._comm.all_gather(inp.view(-1), out=out.view(-1)[:inp.numel() * self.world_size], algo="auto")
+        return out
 
     def custom_all_gather(self, input: torch.Tensor, out=None) -> Optional[torch.Tensor]:
         # the gathered result, not the shard, has to fit the staging buffer's peers
@@ -194,12 +246,16 @@ class CustomAllreduce:
             if out is None:
                 return torch.empty(input.numel() * self.world_size, dtype=input.dtype, device=input.device)
             return out
-        return self._dispatch(self.all_gather, input, out, warm)
+        return self._dispatch(self._fast_all_gather, self.all_gather, input, out, warm)
 
     # ------------------------------------------------------------------- fused
     def attach_communicator(self, comm):
-        """Gives this object a symmetric-heap communicator for the fused ops."""
+        """Uses `comm` (a symmetric-heap communicator over the same ranks) instead of the one
+        made by the constructor, e.g. to share one heap with the rest of the engine."""
+        if self._own_comm and self._comm is not None:
+            self._comm.close()
         self._comm = comm
+        self._own_comm = False
 
     def fused_all_reduce_rmsnorm(self, input: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor,
                                  eps: float = 1e-5, proto: str = "ll"):
@@ -214,10 +270,21 @@ class CustomAllreduce:
 
     # ----------------------------------------------------------------- teardown
     def status(self, clear: bool = True) -> List[int]:
-        """Status words of the last device-side timeout ([0] == 0: none)."""
+        """Status words of the last device-side timeout ([0] == 0: none), of the fast path's
+        communicator when that is in use, else of the pull kernels."""
+        if self.fast:
+            rec = self._comm.status(0, clear)
+            if rec["code"] != 0:
+                return [rec["code"], rec["rank"], rec["peer"], rec["block"], 0, 0, 0, 0]
         return list(ops.custom_ar_status(self._ptr, clear)) if self._ptr else [0] * 8
 
     def close(self):
+        if self._own_comm and self._comm is not None:
+            try:
+                torch.cuda.synchronize()
+                self._comm.close()
+            finally:
+                self._comm, self._own_comm = None, False
         if not self.disabled and self._ptr:
             if ops is not None:
                 ops.dispose(self._ptr)

@@ -18,7 +18,7 @@ _LIB = None
 ALGO_IDS = {
     "ring_standard": 0, "ring_simple": 1, "oneshot": 2, "twoshot": 3, "double_ring": 4, "tree": 5,
     "oneshot_ll": 7, "reduce_scatter": 16, "all_gather": 17, "all_to_all": 18, "exchange": 19,
-    "reduce_scatter_pipelined": 20, "all_to_all_pipelined": 21, "twoshot_pipelined": 22,
+    "reduce_scatter_pipelined": 20, "all_to_all_pipelined": 21,
 }
 DTYPE_IDS = {"float32": 0, "float16": 1, "bfloat16": 2}
 

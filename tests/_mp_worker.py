@@ -131,7 +131,7 @@ def main():
 
     # fused all-reduce + residual + RMSNorm
     hidden = 4096
-    protos = ["ll", "flag"] + (["nvls", "nvls_oneshot"] if comm.has_multicast else [])
+    protos = ["ll", "flag", "ll_twoshot"] + (["nvls", "nvls_oneshot"] if comm.has_multicast else [])
     for rows in (1, 8, 64, 256):
         g = torch.Generator(device="cuda").manual_seed(77 + rank + rows)
         xin = (torch.randn(rows, hidden, device="cuda", generator=g) * 0.5).bfloat16()
@@ -157,7 +157,7 @@ def main():
                 comm.fused_all_reduce_rmsnorm(xi, w, residual=r, out=out, proto=proto)
                 comm.check()
                 torch.testing.assert_close(out.float().cpu(), want, **TOL[torch.bfloat16])
-                if proto == "nvls":  # residual stream stays sharded by row
+                if proto in ("nvls", "ll_twoshot"):  # residual stream stays sharded by row
                     lo = (rows + world - 1) // world * rank
                     hi = min(rows, lo + (rows + world - 1) // world)
                     if hi > lo:
@@ -220,7 +220,7 @@ def main():
         B, kv = 4, 100
         full = LlamaTPDecoder(cfg, world=1, max_batch=B, max_len=160, use_graph=False, full_init=True)
         full.fill_synthetic_kv(kv)
-        protos = ["ll", "flag"] + (["nvls", "nvls_oneshot"] if comm.has_multicast else [])
+        protos = ["ll", "flag", "ll_twoshot"] + (["nvls", "nvls_oneshot"] if comm.has_multicast else [])
         for backend, proto in [("penny", p) for p in protos] + [("penny_unfused", "flag"), ("nccl", "flag")]:
             tp = LlamaTPDecoder(cfg, comm=comm, rank=rank, world=world, max_batch=B, max_len=160,
                                 backend=backend, proto=proto, use_graph=(backend != "nccl"), full_init=True)
@@ -288,51 +288,58 @@ def main():
         assert torch.all(b == float(rank ^ 1))
     check("reference_module_api", run_handle_api)
 
-    # ---- drop-in CustomAllreduce: eager, registered, CUDA-graph capture ----
+    # ---- drop-in CustomAllreduce: eager, registered, CUDA-graph capture; on the symmetric-heap
+    # kernels (default) and on the pull kernels over IPC-registered buffers ----
     from penny.custom_all_reduce import CustomAllreduce
     gloo = dist.new_group(backend="gloo")
-    car = CustomAllreduce(gloo, torch.cuda.current_device())
+    for backend in ("fast", "pull"):
+        os.environ["PENNY_CUSTOM_AR_BACKEND"] = backend
+        car = CustomAllreduce(gloo, torch.cuda.current_device())
+        os.environ.pop("PENNY_CUSTOM_AR_BACKEND")
 
-    def run_custom():
-        assert not car.disabled
-        for dtype in (torch.float32, torch.float16, torch.bfloat16):
-            for n in (8, 4096, 1 << 18, (1 << 20) + 64):
-                g = torch.Generator(device="cuda").manual_seed(99 + rank + n)
-                x = (torch.rand(n, device="cuda", generator=g) * 2 - 1).to(dtype)
-                parts = gather_cpu(x)
-                want = torch.stack([p.float() for p in parts]).sum(0)
-                if not car.should_custom_ar(x):
-                    continue
-                y = car.custom_all_reduce(x)
+        def run_custom(car=car, backend=backend):
+            assert not car.disabled and car.fast == (backend == "fast")
+            for dtype in (torch.float32, torch.float16, torch.bfloat16):
+                for n in (8, 4096, 1 << 18, (1 << 20) + 64):
+                    g = torch.Generator(device="cuda").manual_seed(99 + rank + n)
+                    x = (torch.rand(n, device="cuda", generator=g) * 2 - 1).to(dtype)
+                    parts = gather_cpu(x)
+                    want = torch.stack([p.float() for p in parts]).sum(0)
+                    if not car.should_custom_ar(x):
+                        continue
+                    y = car.custom_all_reduce(x)
+                    assert car.status()[0] == 0
+                    torch.testing.assert_close(y.float().cpu(), want, **TOL[dtype])
+                    if n % world == 0 and (n // world * x.element_size()) % 16 == 0:
+                        rs = car.custom_reduce_scatter(x)
+                        sh = n // world
+                        torch.testing.assert_close(rs[:sh].float().cpu(), want[rank * sh:(rank + 1) * sh], **TOL[dtype])
+                    if n * world * x.element_size() < car.max_size:
+                        ag = car.custom_all_gather(x)
+                        assert torch.equal(ag.cpu(), torch.cat(parts))
+            assert car.custom_all_reduce(torch.ones(3, device="cuda")) is None  # 12 bytes: not a multiple of 16
+        check(f"custom_all_reduce_eager/{backend}", run_custom)
+
+        def run_custom_graph(car=car):
+            for n in (4096, 1 << 19):  # flag-in-data lines; the switch or pushes
+                x = torch.full((n,), float(rank + 1), device="cuda", dtype=torch.bfloat16)
+                with car.capture():
+                    car.custom_all_reduce(x)  # warm-up
+                    torch.cuda.synchronize()
+                    gr = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gr):
+                        y = car.custom_all_reduce(x)
+                        z = car.custom_all_reduce(y)
+                for _ in range(3):
+                    gr.replay()
+                torch.cuda.synchronize()
                 assert car.status()[0] == 0
-                torch.testing.assert_close(y.float().cpu(), want, **TOL[dtype])
-                if n % world == 0 and (n // world * x.element_size()) % 16 == 0:
-                    rs = car.custom_reduce_scatter(x)
-                    sh = n // world
-                    torch.testing.assert_close(rs[:sh].float().cpu(), want[rank * sh:(rank + 1) * sh], **TOL[dtype])
-                if n * world * x.element_size() < car.max_size:
-                    ag = car.custom_all_gather(x)
-                    assert torch.equal(ag.cpu(), torch.cat(parts))
-        assert car.custom_all_reduce(torch.ones(3, device="cuda")) is None  # 12 bytes: not a multiple of 16
-    check("custom_all_reduce_eager", run_custom)
-
-    def run_custom_graph():
-        x = torch.full((4096,), float(rank + 1), device="cuda", dtype=torch.bfloat16)
-        with car.capture():
-            car.custom_all_reduce(x)  # warm-up: allocation only
-            torch.cuda.synchronize()
-            gr = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(gr):
-                y = car.custom_all_reduce(x)
-                z = car.custom_all_reduce(y)
-        for _ in range(3):
-            gr.replay()
+                s = world * (world + 1) / 2
+                assert torch.all(y.float() == s) and torch.all(z.float() == s * world)
+        check(f"custom_all_reduce_graph/{backend}", run_custom_graph)
         torch.cuda.synchronize()
-        assert car.status()[0] == 0
-        s = world * (world + 1) / 2
-        assert torch.all(y.float() == s) and torch.all(z.float() == s * world)
-    check("custom_all_reduce_graph", run_custom_graph)
-    car.close()
+        dist.barrier()
+        car.close()
 
     torch.cuda.synchronize()
     dist.barrier()

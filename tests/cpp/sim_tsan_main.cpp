@@ -14,7 +14,7 @@
 
 int main() {
   // ids as in csrc/algos.h and the simulator's extra collectives
-  const int algos[] = {0, 1, 2, 3, 4, 5, 7, 16, 17, 18, 19, 20, 21, 22};
+  const int algos[] = {0, 1, 2, 3, 4, 5, 7, 16, 17, 18, 19, 20, 21};
   int bad = 0;
   for (int algo : algos)
     for (int world : {2, 4})
