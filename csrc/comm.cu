@@ -494,8 +494,10 @@ void Communicator::exchange(int dtype, void* const* buf, size_t n, const int* pe
 void Communicator::fused_ar_rmsnorm(int dtype, int proto, const void* const* in,
                                     const void* const* residual, const void* weight,
                                     void* const* out, void* const* residual_out, int rows,
-                                    int hidden, float eps, const Tuning& t, cudaStream_t stream) {
+                                    int hidden, float eps, const Tuning& t, cudaStream_t stream, bool pushed) {
   const int es = dtype_size(dtype);
+  if (pushed && (proto != FUSED_PROTO_LL_TWOSHOT || world_ < 2))
+    throw std::runtime_error("penny: pushed inputs are a feature of the LL two-shot fused norm");
   const int nv = views();
   FusedNormArgs a[kMaxRanks];
   memset(a, 0, sizeof(a));
@@ -510,6 +512,7 @@ void Communicator::fused_ar_rmsnorm(int dtype, int proto, const void* const* in,
     a[v].eps = eps;
     a[v].in_heap_off = heap_offset_of(in[v], v);
     a[v].out_heap_off = heap_offset_of(out[v], v);
+    a[v].pushed = pushed ? 1 : 0;
   }
   int threads = t.threads > 0 ? t.threads : std::min(512, std::max(32, (hidden * es / 16 + 31) / 32 * 32));
   if (world_ == 1) {
@@ -536,6 +539,8 @@ void Communicator::fused_ar_rmsnorm(int dtype, int proto, const void* const* in,
   } else {
     Region& r = ensure(proto == FUSED_PROTO_LL || proto == FUSED_PROTO_LL_TWOSHOT ? scratch_ll_ : scratch_,
                        fused_norm_scratch_bytes(proto, rows, hidden, es, world_), "fused norm");
+    if (pushed && (r.off != push_region_.off || r.bytes != push_region_.bytes))
+      throw std::runtime_error("penny: the scratch region changed since fused_norm_push_target; ask for a new target");
     for (int v = 0; v < nv; ++v) {
       a[v].scratch_off = r.off;
       a[v].scratch_bytes = r.bytes;
@@ -543,6 +548,26 @@ void Communicator::fused_ar_rmsnorm(int dtype, int proto, const void* const* in,
     cfg.blocks = t.blocks > 0 ? t.blocks : std::min(max_blocks, rows);
   }
   ckrt(launch_fused_ar_rmsnorm(dtype, proto, ctx_, a, cfg), "fused_ar_rmsnorm");
+}
+
+sm100::DecodePush Communicator::fused_norm_push_target(int rows, int hidden, int elem_size, int view) {
+  if (world_ < 2 || elem_size != 2 || hidden % 8 != 0 || rows < 1)
+    throw std::runtime_error("penny: fused_norm_push_target needs >= 2 ranks, bf16 and hidden % 8 == 0");
+  Region& r = ensure(scratch_ll_, fused_norm_scratch_bytes(FUSED_PROTO_LL_TWOSHOT, rows, hidden, elem_size, world_),
+                     "fused norm");
+  push_region_ = r;
+  sm100::DecodePush p;
+  memset(&p, 0, sizeof(p));
+  for (int k = 0; k < world_; ++k) p.heap[k] = heap_->base(k);
+  const int me = emu_ ? view : rank_;
+  p.call_seq = &reinterpret_cast<const SignalPad*>(heap_->base(me))->call_seq[SEQ_ALL];
+  p.scratch_off = r.off;
+  p.scratch_bytes = r.bytes;
+  p.rank = me;
+  p.world = world_;
+  p.per = (rows + world_ - 1) / world_;
+  p.hv = hidden / 8;
+  return p;
 }
 
 void Communicator::moe_dispatch(int dtype, const MoeArgs* args, const Tuning& t, cudaStream_t stream) {

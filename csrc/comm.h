@@ -22,6 +22,7 @@
 #include "bootstrap.h"
 #include "coll_args.h"
 #include "fused_ops.h"
+#include "gemm_decode_sm100.h"
 #include "symm_heap.h"
 
 namespace penny {
@@ -91,7 +92,11 @@ class Communicator {
   // proto: FusedProto.  Pointer arrays have views() entries.
   void fused_ar_rmsnorm(int dtype, int proto, const void* const* in, const void* const* residual,
                         const void* weight, void* const* out, void* const* residual_out, int rows,
-                        int hidden, float eps, const Tuning& t, cudaStream_t stream);
+                        int hidden, float eps, const Tuning& t, cudaStream_t stream, bool pushed = false);
+  // Where the decode GEMM that feeds fused_ar_rmsnorm(FUSED_PROTO_LL_TWOSHOT, pushed = true) on a
+  // [rows, hidden] tensor puts the rows other ranks own (view: the virtual rank when emulated).
+  // Reserves the scratch region; the pushed call checks that it is still the same one.
+  sm100::DecodePush fused_norm_push_target(int rows, int hidden, int elem_size, int view = 0);
 
   // MoE expert-parallel row exchange; args: views() entries (see MoeArgs).
   void moe_dispatch(int dtype, const MoeArgs* args, const Tuning& t, cudaStream_t stream);
@@ -156,6 +161,7 @@ class Communicator {
   // gathered A of all_gather_gemm: one dedicated region per (M, K), kept for the
   // communicator's lifetime and reused, so alternating shapes do not grow the heap
   std::map<std::pair<int, int>, Region> ag_regions_;
+  Region push_region_;   // scratch the last fused_norm_push_target was given
   std::vector<TuneEntry> tune_[2][2];  // [elem_size == 4][symmetric]
   bool destroyed_ = false;
 };

@@ -277,8 +277,8 @@ struct FusedTwoShotLLNorm {
       const int owner = (int)(row / per), lrow = (int)(row % per);
       bool ok = true;
       if (owner != rank) {
-        // my partial of the row -> its owner
-        for (int v = threadIdx.x; v < HV; v += blockDim.x) {
+        // my partial of the row -> its owner (unless the GEMM that produced it already did)
+        for (int v = threadIdx.x; v < HV && !a.pushed; v += blockDim.x) {
           V16 l0, l1;
           to_lines(ld16(in + row * a.hidden + (size_t)v * E), l0, l1);
           char* dst = c.heap[owner] + base + (((size_t)rank * per + lrow) * HV + v) * 32;

@@ -30,6 +30,8 @@ struct FusedNormArgs {
   size_t scratch_bytes;
   size_t in_heap_off;   // NVLS: offset of `in` in the heap
   size_t out_heap_off;  // NVLS: offset of `out` in the heap
+  int pushed;           // LL two-shot: the producing GEMM already wrote the partial rows of the
+                        // other ranks into their receive lines (DecodePush): nothing to push here
 };
 
 // scratch for the one-shot protocols (both halves)

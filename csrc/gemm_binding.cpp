@@ -7,7 +7,6 @@
 #include <torch/extension.h>
 
 #include "gemm_decode_sm100.h"
-#include "gemm_skinny_sm100.h"
 #include "pdl.h"
 #include "gemm_sm100.h"
 
@@ -44,32 +43,13 @@ void bind_gemm(py::module_& m) {
         (int)out.stride(0), (int)block_n, penny_gemm_error_word(), at::cuda::getCurrentCUDAStream().stream());
     TORCH_CHECK(rc == cudaSuccess, "gemm_bf16: ", cudaGetErrorString(rc));
   }, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("block_n") = 0);
-  // Decode-batch linear: out[B, N] = x[B, K] @ w[N, K]^T for B <= 128, streaming w at HBM
-  // speed on all SMs (stream-K).  silu_pairs: w's rows are blocks of 64 gate + 64 up rows and
-  // out is [B, N / 2] = silu(gate) * up.
-  m.def("gemm_skinny", [](at::Tensor x, at::Tensor w, at::Tensor out, bool silu_pairs) {
-    TORCH_CHECK(x.is_cuda() && w.is_cuda() && out.is_cuda(), "gemm_skinny: CUDA tensors");
-    TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 &&
-                    out.scalar_type() == at::kBFloat16, "gemm_skinny: bf16 only");
-    TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm_skinny: 2-D tensors");
-    TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1, "gemm_skinny: rows must be contiguous");
-    const int64_t B = x.size(0), K = x.size(1), N = w.size(0);
-    TORCH_CHECK(B >= 1 && B <= 128, "gemm_skinny: 1 <= rows of x <= 128 (use gemm_bf16 beyond)");
-    TORCH_CHECK(w.size(1) == K && out.size(0) == B && out.size(1) == (silu_pairs ? N / 2 : N),
-                "gemm_skinny: shape mismatch");
-    const at::cuda::OptionalCUDAGuard guard(x.device());
-    cudaError_t rc = penny::sm100::launch_gemm_skinny(
-        x.data_ptr(), w.data_ptr(), out.data_ptr(), (int)B, (int)N, (int)K, (int)x.stride(0), (int)w.stride(0),
-        (int)out.stride(0), silu_pairs ? 1 : 0, penny_gemm_error_word(), at::cuda::getCurrentCUDAStream().stream());
-    TORCH_CHECK(rc == cudaSuccess, "gemm_skinny: ", cudaGetErrorString(rc));
-  }, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("silu_pairs") = false);
   // Decode-batch linear: out[B, N] = x[B, K] @ w[N, K]^T for B <= 128.  One CTA per (weight tile, K
   // range); the K ranges of a tile are reduced inside a thread-block cluster through distributed shared
   // memory.  pdl: may start (and load w) while the previous kernel on the stream still runs, so w must not
   // be written by that kernel.  silu_pairs: w's rows are blocks of 64 gate + 64 up rows and out is
   // [B, N / 2] = silu(gate) * up.
   m.def("gemm_decode", [](at::Tensor x, at::Tensor w, at::Tensor out, bool silu_pairs, int64_t splits, bool pdl,
-                          int64_t l2_budget, int64_t smem_kb) {
+                          int64_t l2_budget, int64_t smem_kb, c10::optional<at::Tensor> push) {
     TORCH_CHECK(x.is_cuda() && w.is_cuda() && out.is_cuda(), "gemm_decode: CUDA tensors");
     TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 &&
                     out.scalar_type() == at::kBFloat16, "gemm_decode: bf16 only");
@@ -81,14 +61,23 @@ void bind_gemm(py::module_& m) {
                 "gemm_decode: shape mismatch");
     TORCH_CHECK(splits >= 0 && splits <= 8, "gemm_decode: 0 <= splits <= 8");
     const at::cuda::OptionalCUDAGuard guard(x.device());
+    // push: the bytes of a DecodePush from comm_fused_norm_push_target (rows other ranks own go to them)
+    penny::sm100::DecodePush pd;
+    const penny::sm100::DecodePush* pp = nullptr;
+    if (push.has_value()) {
+      TORCH_CHECK(push->device().is_cpu() && push->scalar_type() == at::kByte && push->is_contiguous() &&
+                      push->numel() == (int64_t)sizeof(pd), "gemm_decode: push must come from comm_fused_norm_push_target");
+      memcpy(&pd, push->data_ptr(), sizeof(pd));
+      pp = &pd;
+    }
     cudaError_t rc = penny::sm100::launch_gemm_decode(
         x.data_ptr(), w.data_ptr(), out.data_ptr(), (int)B, (int)N, (int)K, (int)x.stride(0), (int)w.stride(0),
-        (int)out.stride(0), silu_pairs ? 1 : 0, (int)splits, pdl, (long long)l2_budget, (int)smem_kb,
+        (int)out.stride(0), silu_pairs ? 1 : 0, (int)splits, pdl, (long long)l2_budget, (int)smem_kb, pp,
         penny_gemm_error_word(),
         at::cuda::getCurrentCUDAStream().stream());
     TORCH_CHECK(rc == cudaSuccess, "gemm_decode: ", cudaGetErrorString(rc));
   }, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("silu_pairs") = false, py::arg("splits") = 0,
-     py::arg("pdl") = true, py::arg("l2_budget") = -1, py::arg("smem_kb") = 0);
+     py::arg("pdl") = true, py::arg("l2_budget") = -1, py::arg("smem_kb") = 0, py::arg("push") = py::none());
   m.def("gemm_decode_splits", [](int64_t B, int64_t N, int64_t K) {
     return penny::sm100::gemm_decode_splits((int)B, (int)N, (int)K);
   });

@@ -45,6 +45,7 @@
 #include <map>
 #include <mutex>
 
+#include "all_reduce_oneshot.cuh"
 #include "decode_gemm_plan.h"
 #include "gemm_kernel_sm100.cuh"
 #include "gemm_sm100.h"
@@ -91,6 +92,7 @@ struct DecodeArgs {
   int k_stagger;    // 1: tiles start their K range at different offsets
   int stamps;       // 1: record timestamps
   int epi;          // DECODE_EPI_*
+  DecodePush push;  // world == 0: plain store
 };
 
 template <int BT>
@@ -362,6 +364,14 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       const int n_out = silu ? a.N / 2 : a.N;
       const int n_tile0 = tile * (silu ? kBlockM / 2 : kBlockM);
       const bool vec_ok = (a.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.out) & 15u) == 0);
+      // push mode: the call number of the all-reduce that follows (final: the predecessor has
+      // finished) selects the scratch half and stamps the lines
+      unsigned long long push_seq = 0;
+      size_t push_base = 0;
+      if (a.push.world > 0) {
+        push_seq = *reinterpret_cast<const volatile unsigned long long*>(a.push.call_seq);
+        push_base = scratch_half(a.push.scratch_off, a.push.scratch_bytes, push_seq);
+      }
       for (int idx = lane; idx < (hi - lo) * groups; idx += 32) {
         const int j = lo + idx / groups, g = q * groups + idx % groups;
         // sum over the cluster of rows r0 .. r0 + 7 of column j
@@ -395,7 +405,21 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           o.y = pack_bf16x2(__float_as_uint(v[2]), __float_as_uint(v[3]));
           o.z = pack_bf16x2(__float_as_uint(v[4]), __float_as_uint(v[5]));
           o.w = pack_bf16x2(__float_as_uint(v[6]), __float_as_uint(v[7]));
-          *reinterpret_cast<uint4*>(dst) = o;
+          const int owner = a.push.world > 0 ? j / a.push.per : -1;
+          if (owner >= 0 && owner != a.push.rank) {
+            // a row another rank reduces: straight into that rank's receive lines of the coming
+            // all-reduce (flag-in-data: two 16-byte lines carry the 16 bytes and the call's stamp)
+            const uint32_t e = ll_flag(push_seq);
+            V16 l0, l1;
+            l0.w[0] = o.x; l0.w[1] = e; l0.w[2] = o.y; l0.w[3] = e;
+            l1.w[0] = o.z; l1.w[1] = e; l1.w[2] = o.w; l1.w[3] = e;
+            char* line = a.push.heap[owner] + push_base +
+                         (((size_t)a.push.rank * a.push.per + (j - owner * a.push.per)) * a.push.hv + n0 / 8) * 32;
+            st16_volatile(line, l0);
+            st16_volatile(line + 16, l1);
+          } else {
+            *reinterpret_cast<uint4*>(dst) = o;
+          }
         } else {
           for (int k = 0; k < 8; ++k)
             if (n0 + k < n_out) dst[k] = __float2bfloat16_rn(v[k]);
@@ -462,7 +486,8 @@ const int* decode_capacity(int sms) {
 
 template <int BT>
 cudaError_t launch_decode_bt(const void* x, const void* w, void* out, int B, int N, int K, int ldx, int ldw, int ldo,
-                             int epi, int splits, bool pdl, long long l2_budget, int smem_kb, int sms, uint32_t* error_word,
+                             int epi, int splits, bool pdl, long long l2_budget, int smem_kb, const DecodePush* push, int sms,
+                             uint32_t* error_word,
                              cudaStream_t stream) {
   using Cfg = DecodeCfg<BT>;
   CUtensorMap mw, mx;
@@ -482,6 +507,10 @@ cudaError_t launch_decode_bt(const void* x, const void* w, void* out, int B, int
   splits = std::max(1, std::min(splits, std::min(kDecodeMaxSplits, a.num_kb)));
   a.splits = splits;
   a.epi = epi;
+  if (push != nullptr)
+    a.push = *push;
+  else
+    a.push.world = 0;
   // ring depth: what fits next to the receive area in ~106 KB (two kernels per SM); with a
   // 128-wide batch tile one kernel per SM and as deep as the range needs
   const int kb_per = (a.num_kb + splits - 1) / splits;
@@ -512,21 +541,24 @@ cudaError_t launch_decode_bt(const void* x, const void* w, void* out, int B, int
 
 cudaError_t launch_gemm_decode(const void* x, const void* w, void* out, int B, int N, int K, int ldx, int ldw,
                                int ldo, int epi, int splits, bool pdl, long long l2_budget_bytes,
-                               int smem_kb, uint32_t* error_word, cudaStream_t stream) {
+                               int smem_kb, const DecodePush* push, uint32_t* error_word, cudaStream_t stream) {
   if (B <= 0 || B > 128 || N <= 0 || K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0)
     return cudaErrorInvalidValue;
   if (epi != DECODE_EPI_PLAIN && epi != DECODE_EPI_SILU_PAIRS) return cudaErrorInvalidValue;
   if (epi == DECODE_EPI_SILU_PAIRS && N % kBlockM != 0) return cudaErrorInvalidValue;
   if ((N + kBlockM - 1) / kBlockM > 65535) return cudaErrorInvalidValue;
+  if (push != nullptr && (push->world < 2 || push->world > 8 || epi != DECODE_EPI_PLAIN || N % 8 != 0 || ldo % 8 != 0 ||
+                          push->hv * 8 != N || push->per < 1 || (reinterpret_cast<uintptr_t>(out) & 15u) != 0))
+    return cudaErrorInvalidValue;
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (l2_budget_bytes < 0) l2_budget_bytes = (long long)32 << 20;
   if (B <= 32)
-    return launch_decode_bt<32>(x, w, out, B, N, K, ldx, ldw, ldo, epi, splits, pdl, l2_budget_bytes, smem_kb, sms, error_word, stream);
+    return launch_decode_bt<32>(x, w, out, B, N, K, ldx, ldw, ldo, epi, splits, pdl, l2_budget_bytes, smem_kb, push, sms, error_word, stream);
   if (B <= 64)
-    return launch_decode_bt<64>(x, w, out, B, N, K, ldx, ldw, ldo, epi, splits, pdl, l2_budget_bytes, smem_kb, sms, error_word, stream);
-  return launch_decode_bt<128>(x, w, out, B, N, K, ldx, ldw, ldo, epi, splits, pdl, l2_budget_bytes, smem_kb, sms, error_word, stream);
+    return launch_decode_bt<64>(x, w, out, B, N, K, ldx, ldw, ldo, epi, splits, pdl, l2_budget_bytes, smem_kb, push, sms, error_word, stream);
+  return launch_decode_bt<128>(x, w, out, B, N, K, ldx, ldw, ldo, epi, splits, pdl, l2_budget_bytes, smem_kb, push, sms, error_word, stream);
 }
 
 int gemm_decode_stamps(unsigned long long* out, int max_ctas) {

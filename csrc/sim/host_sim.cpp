@@ -24,7 +24,6 @@
 
 #include "../algos.h"
 #include "../gemm_tile_order.h"
-#include "../skinny_order.h"
 #include "../decode_gemm_plan.h"
 #include "../all_reduce_oneshot.cuh"
 #include "../all_reduce_ring.cuh"
@@ -330,21 +329,6 @@ void penny_sched_split_span(unsigned long long V, int parts, int i, unsigned lon
   *e = s.end;
 }
 int penny_status_words() { return penny::kStatusWords; }
-// The i-th segment of CTA `cta` of the weight-streaming GEMM's stream-K split:
-// out = {tile, kb0, kb1, c_lo, c_hi, slot}; 0 when the CTA has fewer segments.
-int penny_skinny_segment(int tiles, int num_kb, int ctas, int cta, int i, int* out) {
-  penny::sm100::SkinnyPlan p{tiles, num_kb, ctas};
-  long long cur = penny::sm100::skinny_begin(p, cta);
-  penny::sm100::SkinnySeg s{};
-  for (int k = 0; k <= i; ++k)
-    if (!penny::sm100::skinny_next(p, cta, cur, s)) return 0;
-  out[0] = s.tile; out[1] = s.kb0; out[2] = s.kb1; out[3] = s.c_lo; out[4] = s.c_hi; out[5] = s.slot;
-  return 1;
-}
-int penny_skinny_slot_of(int tiles, int num_kb, int ctas, int cta, int tile) {
-  penny::sm100::SkinnyPlan p{tiles, num_kb, ctas};
-  return penny::sm100::skinny_slot_of(p, cta, tile);
-}
 // Work split of the decode GEMM (decode_gemm_plan.h): out = {kb0, kb1, slice, recv_floats}
 // of CTA `r` of a cluster of `splits` working on a bt-wide batch tile.
 void penny_decode_plan(int num_kb, int splits, int r, int bt, long long* out) {

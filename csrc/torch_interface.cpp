@@ -326,7 +326,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                     std::vector<at::Tensor> residual, at::Tensor weight,
                                     std::vector<at::Tensor> out, std::vector<at::Tensor> residual_out,
                                     double eps, int proto, int blocks, int threads, bool symmetric,
-                                    int symmetric_out_arg) {
+                                    int symmetric_out_arg, bool pushed) {
     Communicator* c = as_comm(h);
     const int nv = c->views();
     // symmetric: the inputs sit at one heap offset on every rank; symmetric_out: the outputs do
@@ -372,11 +372,19 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     c->fused_ar_rmsnorm(dtype_of(in[0]), proto, ip.data(), residual.empty() ? nullptr : rp.data(),
                         weight.data_ptr(), op.data(), residual_out.empty() ? nullptr : rop.data(),
                         rows, hidden, (float)eps,
-                        make_tuning(blocks, threads, 1, 0, symmetric, symmetric_out), current_stream());
+                        make_tuning(blocks, threads, 1, 0, symmetric, symmetric_out), current_stream(), pushed);
   }, py::arg("comm"), py::arg("inputs"), py::arg("residual"), py::arg("weight"),
      py::arg("outputs"), py::arg("residual_out"), py::arg("eps") = 1e-5, py::arg("proto") = 0,
      py::arg("blocks") = 0, py::arg("threads") = 0, py::arg("symmetric") = false,
-     py::arg("symmetric_out") = -1);
+     py::arg("symmetric_out") = -1, py::arg("pushed") = false);
+  // The epilogue target (a DecodePush, as bytes in a CPU tensor) for gemm_decode(push=...) feeding
+  // comm_fused_ar_rmsnorm(proto = LL two-shot, pushed = true) on a [rows, hidden] bf16 tensor.
+  m.def("comm_fused_norm_push_target", [](int64_t h, int64_t rows, int64_t hidden, int64_t view) {
+    const penny::sm100::DecodePush p = as_comm(h)->fused_norm_push_target((int)rows, (int)hidden, 2, (int)view);
+    auto t = torch::empty({(int64_t)sizeof(p)}, torch::TensorOptions().dtype(torch::kUInt8));
+    memcpy(t.data_ptr(), &p, sizeof(p));
+    return t;
+  }, py::arg("comm"), py::arg("rows"), py::arg("hidden"), py::arg("view") = 0);
 
   // out = rmsnorm(x + residual) * weight without communication (world size 1)
   m.def("add_rmsnorm", [](at::Tensor x, c10::optional<at::Tensor> residual, at::Tensor weight,

@@ -93,6 +93,12 @@ class LlamaTPDecoder:
             else:
                 proto = "flag"
         self.proto = proto
+        # flag-in-data two-shot: the o_proj / down GEMMs write the rows other ranks own straight into
+        # those ranks' receive lines, the all-reduce kernel only polls, reduces and sends back
+        self._push = None
+        if (comm is not None and world > 1 and backend == "penny" and proto == "ll_twoshot" and linears == "penny"
+                and max_batch <= 128 and hasattr(comm, "fused_norm_push_target")):
+            self._push = comm.fused_norm_push_target(max_batch, H)
         self._init_weights(seed, full_init)
 
         def buf(*shape, dtype=dt, heap=False):
@@ -244,7 +250,7 @@ class LlamaTPDecoder:
             ops.add_rmsnorm(part, self.residual, weight, self.x, self.residual, self.cfg.eps)
         elif self.backend == "penny":
             self.comm.fused_all_reduce_rmsnorm(part, weight, residual=self.residual, out=self.x,
-                                               eps=self.cfg.eps, proto=self.proto)
+                                               eps=self.cfg.eps, proto=self.proto, pushed=self._push is not None)
         elif self.backend == "penny_unfused":
             self.comm.all_reduce(part, out=part)
             ops.add_rmsnorm(part, self.residual, weight, self.x, self.residual, self.cfg.eps)
@@ -253,11 +259,11 @@ class LlamaTPDecoder:
             dist.all_reduce(part, group=self.pg)
             ops.add_rmsnorm(part, self.residual, weight, self.x, self.residual, self.cfg.eps)
 
-    def _linear(self, x, w, out, silu_pairs=False, smem_kb=0):
+    def _linear(self, x, w, out, silu_pairs=False, smem_kb=0, push=None):
         """out = x @ w^T on this library's decode GEMM, 128 rows of x per launch."""
         B = x.shape[0]
         for r in range(0, B, 128):
-            ops.gemm_decode(x[r:r + 128], w, out[r:r + 128], silu_pairs, 0, self.pdl, -1, smem_kb)
+            ops.gemm_decode(x[r:r + 128], w, out[r:r + 128], silu_pairs, 0, self.pdl, -1, smem_kb, push)
 
     def _step_impl(self):
         cfg = self.cfg
@@ -272,13 +278,13 @@ class LlamaTPDecoder:
                                        self.workspace, self.Hq, self.Hkv, self.splits, self.scale, cfg.rope_theta,
                                        self.pdl)
             if self.linears == "penny":
-                self._linear(self.attn, L["wo"], self.parts[0])
+                self._linear(self.attn, L["wo"], self.parts[0], push=self._push)
             else:
                 torch.matmul(self.attn, L["wo"].t(), out=self.parts[0])
             self._reduce_norm(self.parts[0], L["norm2"])
             if self.linears == "penny":
                 self._linear(self.x, L["wgu"], self.act, silu_pairs=True)
-                self._linear(self.act, L["wdown"], self.parts[1])
+                self._linear(self.act, L["wdown"], self.parts[1], push=self._push)
             else:
                 torch.matmul(self.x, L["wgu_cat"].t(), out=self.gu)
                 ops.silu_mul(self.gu, self.act)

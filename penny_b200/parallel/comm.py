@@ -318,7 +318,8 @@ class Communicator:
 
     def fused_all_reduce_rmsnorm(self, inp: TensorOrList, weight: torch.Tensor, residual: Optional[TensorOrList] = None,
                                  out: Optional[TensorOrList] = None, residual_out: Optional[TensorOrList] = None,
-                                 eps: float = 1e-5, proto: str = "ll", blocks: int = 0, threads: int = 0):
+                                 eps: float = 1e-5, proto: str = "ll", blocks: int = 0, threads: int = 0,
+                                 pushed: bool = False):
         """out = rmsnorm(all_reduce(inp) + residual) * weight; residual_out = all_reduce(inp) + residual.
 
         proto: "auto" (the measured table, restricted to what these tensors allow),
@@ -327,7 +328,9 @@ class Communicator:
         "nvls" (switch reduction, rows sharded over the ranks, result multicast: `inp` and `out`
         must come from `empty()`; each rank keeps the residual of its own rows only) or
         "nvls_oneshot" (every rank pulls all rows switch-reduced: `inp` from `empty()`, and
-        consecutive calls must alternate between two input buffers, see csrc/fused_ar_rmsnorm.cu)."""
+        consecutive calls must alternate between two input buffers, see csrc/fused_ar_rmsnorm.cu).
+        pushed=True ("ll_twoshot" only): the GEMM that produced `inp` was given `fused_norm_push_target`
+        and has already written the rows other ranks own into their receive lines."""
         ins = self._as_list(inp)
         outs = self._as_list(out) if out is not None else [torch.empty_like(x) for x in ins]
         res = self._as_list(residual) if residual is not None else []
@@ -339,8 +342,16 @@ class Communicator:
         else:
             rout = res  # in place on the residual stream
         ops.comm_fused_ar_rmsnorm(self._h, ins, res, weight, outs, rout, float(eps), PROTOS[proto],
-                                  blocks, threads, self.is_symmetric(ins), int(self.is_symmetric(outs)))
+                                  blocks, threads, self.is_symmetric(ins), int(self.is_symmetric(outs)), bool(pushed))
         return self._ret(outs), (self._ret(rout) if rout else None)
+
+    def fused_norm_push_target(self, rows: int, hidden: int, view: int = 0) -> torch.Tensor:
+        """Epilogue target for `ops.gemm_decode(..., push=target)`: the row-parallel linear in front of a
+        `fused_all_reduce_rmsnorm(proto="ll_twoshot", pushed=True)` on a [rows, hidden] bf16 tensor then
+        writes the rows another rank owns straight into that rank's receive lines (flag-in-data), and the
+        all-reduce kernel starts by polling instead of pushing.  Reserves the all-reduce's scratch; ask
+        again if another flag-in-data collective with a larger footprint has run in between."""
+        return ops.comm_fused_norm_push_target(self._h, int(rows), int(hidden), int(view))
 
     # ---------------------------------------------------------------------- MoE
     def moe_dispatch(self, x, order, expert_of_sorted, send_off, dst_base, dst_row_of_pair, recv, meta,

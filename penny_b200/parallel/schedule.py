@@ -114,22 +114,6 @@ def gemm_pair_work(tiles_m: int, tiles_n: int, npairs: int, num_kb: int, pair: i
     return dict(zip(("tile", "kb0", "kb1", "seg", "split_s", "split_first"), list(out)))
 
 
-def skinny_segments(tiles: int, num_kb: int, ctas: int, cta: int):
-    """Segments (dicts: tile, kb0, kb1, c_lo, c_hi, slot) of CTA `cta` in the stream-K split of the
-    weight-streaming decode GEMM (csrc/skinny_order.h)."""
-    lib = sim_lib()
-    out = (ctypes.c_int * 6)()
-    segs, i = [], 0
-    while lib.penny_skinny_segment(tiles, num_kb, ctas, cta, i, out):
-        segs.append(dict(zip(("tile", "kb0", "kb1", "c_lo", "c_hi", "slot"), list(out))))
-        i += 1
-    return segs
-
-
-def skinny_slot_of(tiles: int, num_kb: int, ctas: int, cta: int, tile: int) -> int:
-    return sim_lib().penny_skinny_slot_of(tiles, num_kb, ctas, cta, tile)
-
-
 def decode_plan(num_kb: int, splits: int, r: int, bt: int = 64):
     """K range and reduction layout of CTA `r` in a cluster of `splits` of the decode GEMM
     (csrc/decode_gemm_plan.h): dict(kb0, kb1, slice, recv_floats)."""

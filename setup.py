@@ -35,7 +35,6 @@ CUDA_SOURCES = [
     "csrc/decode_attention_fused.cu",
     "csrc/gemm_sm100.cu",
     "csrc/gemm_fused_sm100.cu",
-    "csrc/gemm_skinny_sm100.cu",
     "csrc/gemm_decode_sm100.cu",
     "csrc/moe_dispatch_combine.cu",
 ]

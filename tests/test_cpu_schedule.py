@@ -184,41 +184,6 @@ def test_cpp_schedule_properties(tmp_path):
     assert "schedule_test ok" in out.stdout
 
 
-@pytest.mark.parametrize("tiles,num_kb,ctas", [(32, 64, 148), (48, 64, 148), (224, 64, 148), (32, 224, 148),
-                                               (1002, 64, 148), (1, 3, 3), (5, 7, 148), (6, 28, 148), (3, 1, 2)])
-def test_skinny_stream_k_split(tiles, num_kb, ctas):
-    """Stream-K split of the decode GEMM: every (tile, K step) belongs to exactly one
-    CTA; CTA loads differ by at most one K step; the CTAs that share a tile are
-    exactly [c_lo, c_hi]; a CTA's partial segments use distinct slots and
-    skinny_slot_of finds them again."""
-    from penny_b200.parallel import schedule
-    ctas = min(ctas, tiles * num_kb)
-    owner = {}
-    loads = []
-    for c in range(ctas):
-        segs = schedule.skinny_segments(tiles, num_kb, ctas, c)
-        loads.append(sum(s["kb1"] - s["kb0"] for s in segs))
-        partial_slots = []
-        for s in segs:
-            for kb in range(s["kb0"], s["kb1"]):
-                assert (s["tile"], kb) not in owner
-                owner[(s["tile"], kb)] = c
-            assert s["c_lo"] <= c <= s["c_hi"]
-            if s["c_lo"] != s["c_hi"]:
-                partial_slots.append(s["slot"])
-                assert schedule.skinny_slot_of(tiles, num_kb, ctas, c, s["tile"]) == s["slot"]
-            else:
-                assert (s["kb0"], s["kb1"]) == (0, num_kb)
-        assert len(partial_slots) == len(set(partial_slots)) <= 2
-    assert len(owner) == tiles * num_kb
-    assert max(loads) - min(loads) <= 1
-    for t in range(tiles):
-        sharers = sorted({owner[(t, kb)] for kb in range(num_kb)})
-        c = owner[(t, 0)]
-        seg = [s for s in schedule.skinny_segments(tiles, num_kb, ctas, c) if s["tile"] == t][0]
-        assert sharers == list(range(seg["c_lo"], seg["c_hi"] + 1))
-
-
 @pytest.mark.parametrize("num_kb,splits,bt", [(64, 8, 64), (64, 3, 64), (8, 4, 64), (28, 5, 64), (224, 7, 64),
                                               (64, 6, 32), (7, 7, 128), (1, 1, 64), (13, 2, 128)])
 def test_decode_gemm_cluster_split(num_kb, splits, bt):

@@ -272,3 +272,40 @@ def test_poisoned_scratch_never_reaches_a_result():
             torch.testing.assert_close(out[0].float(), want, atol=6e-2, rtol=3e-2)
     finally:
         comm.close()
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_gemm_push_into_ll_twoshot_fused_norm(comms, world):
+    """A row-parallel decode GEMM whose epilogue writes the rows other ranks own straight into their
+    flag-in-data receive lines, followed by the all-reduce + RMSNorm that only polls: same result as the
+    fp32 oracle and as the unfused path, twice in a row (both scratch halves, new stamps)."""
+    from penny_b200._ext import ops
+    comm = comms(world)
+    hidden, K = 1024, 512
+    for rows in (64, 5, 37):
+        g = torch.Generator(device="cuda").manual_seed(rows + world)
+        xs = [(torch.randn(rows, K, device="cuda", generator=g) * 0.5).bfloat16() for _ in range(world)]
+        ws = [(torch.randn(hidden, K, device="cuda", generator=g) * 0.05).bfloat16() for _ in range(world)]
+        res = torch.randn(rows, hidden, device="cuda", generator=g).bfloat16()
+        w = (torch.rand(hidden, device="cuda", generator=g) + 0.5).bfloat16()
+        parts_ref = [(x.float() @ wt.float().t()).bfloat16() for x, wt in zip(xs, ws)]
+        z = torch.stack([p.float() for p in parts_ref]).sum(0) + res.float()
+        want = z * torch.rsqrt(z.pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()
+        targets = [comm.fused_norm_push_target(rows, hidden, view=v) for v in range(world)]
+        for rep in range(2):
+            parts = [torch.full((rows, hidden), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+            for v in range(world):
+                ops.gemm_decode(xs[v], ws[v], parts[v], False, 0, True, -1, 0, targets[v])
+            assert ops.gemm_error() == 0
+            outs, routs = comm.fused_all_reduce_rmsnorm(parts, w, residual=[res.clone() for _ in range(world)],
+                                                        proto="ll_twoshot", pushed=True)
+            comm.check()
+            per = -(-rows // world)
+            for r in range(world):
+                torch.testing.assert_close(outs[r].float(), want, atol=8e-2, rtol=3e-2)
+                lo, hi = min(rows, r * per), min(rows, (r + 1) * per)
+                torch.testing.assert_close(routs[r][lo:hi].float(), z[lo:hi], atol=8e-2, rtol=3e-2)
+                # rows this rank owns were stored locally, the others never touched `part`
+                assert torch.isfinite(parts[r][lo:hi].float()).all()
+                if lo > 0:
+                    assert torch.isnan(parts[r][:lo].float()).all()
