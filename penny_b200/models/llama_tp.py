@@ -62,6 +62,13 @@ class LlamaConfig:
         return cls(hidden=512, layers=2, heads=8, kv_heads=2, head_dim=128, ffn=1024, vocab=2048)
 
 
+# world size -> largest batch for which the decode step with proto="ll_twoshot" and the GEMM epilogue
+# push was measured faster than with the transport the stand-alone table picks (8 x B200, Llama-3-8B
+# shapes, kv 2048: batch 1 2.01 vs 2.21 ms, batch 8 2.13 vs 2.31, batch 64 2.70 vs 2.80-2.88; at
+# batch 256 the switch two-shot wins, 5.84 vs 7.39 ms; at 2 GPUs plain "ll" wins, 4.30 vs 4.40 ms).
+PUSHED_STEP_WINS = {8: 128}
+
+
 class LlamaTPDecoder:
     def __init__(self, cfg: LlamaConfig, comm=None, rank: int = 0, world: int = 1, max_batch: int = 64,
                  max_len: int = 2560, backend: str = "penny", proto: str = "auto", seed: int = 0,
@@ -82,10 +89,16 @@ class LlamaTPDecoder:
         dt = torch.bfloat16
         D, H = cfg.head_dim, cfg.hidden
         if proto == "auto":
-            # the measured table when it covers this shape, else: flag-in-data lines for a handful of
-            # rows, the switch (when bound) or flag barriers beyond that
-            if comm is not None and world > 1 and hasattr(comm, "pick_fused_proto"):
-                proto = comm.pick_fused_proto(max_batch, H, dt)
+            # 1. where the row-parallel GEMMs can write into the all-reduce's receive lines and that was
+            #    measured to win the whole step (PUSHED_STEP_WINS), the pushed flag-in-data two-shot;
+            # 2. else the measured table of the stand-alone fused kernel, when it covers this shape;
+            # 3. else flag-in-data lines for a handful of rows, the switch (when bound) or flag barriers
+            can_push = (comm is not None and world > 1 and backend == "penny" and linears == "penny"
+                        and hasattr(comm, "fused_norm_push_target") and not getattr(comm, "emulated", False))
+            if can_push and max_batch <= PUSHED_STEP_WINS.get(world, 0):
+                proto = "ll_twoshot"
+            elif comm is not None and world > 1 and hasattr(comm, "pick_fused_proto"):
+                proto = comm.pick_fused_proto(max_batch, H, dt, alternating_inputs=True)  # self.parts
             elif max_batch <= 16:
                 proto = "ll"
             elif comm is not None and getattr(comm, "has_multicast", False):

@@ -85,6 +85,7 @@ class Communicator:
         # measured (op, world, dtype, memory class, size) -> algorithm table; its all-reduce rows
         # also go to the native communicator, so "auto" means the same through every entry point
         self.tuner = Tuner.load()
+        self._pick_cache = {}
         self._install_tuning()
 
     def _install_tuning(self):
@@ -101,6 +102,7 @@ class Communicator:
     def set_tuner(self, tuner: Tuner):
         """Replaces the algorithm table (e.g. one just built by Tuner.from_sweep)."""
         self.tuner = tuner
+        self._pick_cache = {}
         self._install_tuning()
 
     # ------------------------------------------------------------------ creation
@@ -181,19 +183,30 @@ class Communicator:
         return ALGO_NAMES[ops.comm_pick_algo(self._h, dt, int(numel), bool(symmetric))]
 
     def _pick(self, op: str, nbytes: int, dtype, symmetric: bool) -> Optional[str]:
-        return self.tuner.pick(op, nbytes, self.world_size, dtype, symmetric, self.has_multicast)
+        """Table lookup, remembered per (op, size, dtype, memory class): an eager call pays a dict hit."""
+        key = (op, nbytes, dtype, symmetric)
+        hit = self._pick_cache.get(key, self)
+        if hit is self:
+            hit = self._pick_cache[key] = self.tuner.pick(op, nbytes, self.world_size, dtype, symmetric,
+                                                          self.has_multicast)
+        return hit
 
     def pick_fused_proto(self, rows: int, hidden: int, dtype=torch.bfloat16, symmetric_in: bool = True,
-                         symmetric_out: bool = True) -> str:
+                         symmetric_out: bool = True, alternating_inputs: bool = False) -> str:
         """Transport of fused_all_reduce_rmsnorm(proto="auto"): the measured table when it has an
         entry that these tensors allow, else a handful of rows -> flag-in-data lines, heap tensors ->
-        the switch, anything else -> pushes + a flag barrier."""
+        the switch, anything else -> pushes + a flag barrier.
+        alternating_inputs: the caller promises that consecutive calls read different input buffers,
+        which the one-shot switch transport needs (it has no barrier after the reduction); without
+        the promise the table's "nvls_oneshot" rows are served by "nvls"."""
         nbytes = rows * hidden * torch.empty((), dtype=dtype).element_size()
         mc = self.has_multicast and not self.emulated
 
         def allowed(p):
             return p in ("ll", "flag", "ll_twoshot") or (mc and symmetric_in and (symmetric_out or p == "nvls_oneshot"))
         p = self._pick("fused_norm", nbytes, dtype, symmetric_in)
+        if p == "nvls_oneshot" and not alternating_inputs:
+            p = "nvls" if rows > 16 else "ll"
         if p in PROTOS and allowed(p):
             return p
         if rows <= 16:

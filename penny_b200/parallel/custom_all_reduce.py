@@ -73,6 +73,7 @@ class CustomAllreduce:
         self._ptr = 0
         self._comm = None
         self._own_comm = False
+        self._fast_cache = {}
         if not custom_ar or not torch.cuda.is_available():
             logger.info("Custom allreduce is disabled because of missing custom allreduce library or GPU")
             return
@@ -200,10 +201,12 @@ class CustomAllreduce:
             out = torch.empty_like(inp)
         return self._run(ops.all_reduce, inp, out, registered)
 
+    # The fast path goes straight to the extension: the tensors of a serving engine are ordinary
+    # (non-heap) memory, so the memory class is known, and the table lookup is remembered per size.
     def _fast_all_reduce(self, inp, out):
         if out is None:
             out = torch.empty_like(inp)
-        self._comm.all_reduce(inp.view(-1), out=out.view(-1), algo="auto")
+        ops.comm_all_reduce(self._comm._h, [inp.view(-1)], [out.view(-1)], -1, 0, 0, 1, 0, False, False)
         return out
 
     def custom_all_reduce(self, input: torch.Tensor, out=None) -> Optional[torch.Tensor]:
@@ -216,11 +219,26 @@ class CustomAllreduce:
             out = torch.empty_like(inp)
         return self._run(ops.reduce_scatter, inp, out, registered)
 
+    def _fast_algo(self, op, nbytes, dtype, allowed):
+        key = (op, nbytes, dtype)
+        algo = self._fast_cache.get(key)
+        if algo is None:
+            algo = self._comm._pick(op, nbytes, dtype, False) or "push"
+            if algo not in allowed:
+                algo = "push"
+            self._fast_cache[key] = algo
+        return algo
+
     def _fast_reduce_scatter(self, inp, out):
         if out is None:
             out = torch.empty_like(inp)
         shard = inp.numel() // self.world_size
-        self._comm.reduce_scatter(inp.view(-1), out=out.view(-1)[:shard], algo="auto")
+        nbytes = shard * inp.element_size()
+        algo = self._fast_algo("reduce_scatter", nbytes, inp.dtype,
+                               ("push", "pipelined", "nvls") if nbytes % 16 == 0 and self._comm.has_multicast
+                               else ("push", "pipelined"))
+        ops.comm_reduce_scatter(self._comm._h, [inp.view(-1)], [out.view(-1)[:shard]], algo == "nvls", 0, 0, False,
+                                algo == "pipelined")
         return out
 
     def custom_reduce_scatter(self, input: torch.Tensor, out=None) -> Optional[torch.Tensor]:
@@ -235,9 +253,11 @@ class CustomAllreduce:
         return self._run(ops.all_gather, inp, out, registered)
 
     def _fast_all_gather(self, inp, out):
+        n = inp.numel()
         if out is None:
-            out = torch.empty(inp.numel() * self.world_size, dtype=inp.dtype, device=inp.device)
-        self._comm.all_gather(inp.view(-1), out=out.view(-1)[:inp.numel() * self.world_size], algo="auto")
+            out = torch.empty(n * self.world_size, dtype=inp.dtype, device=inp.device)
+        # the multicast all-gather needs an output in the heap: ordinary outputs take the pushes
+        ops.comm_all_gather(self._comm._h, [inp.view(-1)], [out.view(-1)[:n * self.world_size]], False, 0, 0, False)
         return out
 
     def custom_all_gather(self, input: torch.Tensor, out=None) -> Optional[torch.Tensor]:

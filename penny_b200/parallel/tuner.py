@@ -42,8 +42,8 @@ Rows = List[Tuple[Optional[int], str]]
 FALLBACK: Dict[str, dict] = {
     "all_reduce": {
         "2": {"bf16": {"any": [(64 << 10, "oneshot_ll"), (2 << 20, "oneshot"), (None, "twoshot")]}},
-        "4": {"bf16": {"any": [(32 << 10, "oneshot_ll"), (None, "nvls")]}},
-        "8": {"bf16": {"any": [(32 << 10, "oneshot_ll"), (None, "nvls")]}},
+        "4": {"bf16": {"any": [(64 << 10, "oneshot_ll"), (None, "nvls")]}},
+        "8": {"bf16": {"any": [(64 << 10, "oneshot_ll"), (None, "nvls")]}},
     },
 }
 
@@ -124,6 +124,10 @@ class Tuner:
                 with open(cand) as f:
                     raw = json.load(f)
                 if isinstance(raw, dict) and any(op in raw for op in OPS):
+                    # (op, world) pairs the file has no sweep for keep the fallback rows
+                    for op, per_world in json.loads(json.dumps(FALLBACK)).items():
+                        for world, per_dt in per_world.items():
+                            raw.setdefault(op, {}).setdefault(world, per_dt)
                     return cls(raw, source=cand)
             except (OSError, ValueError):
                 continue
