@@ -25,9 +25,16 @@ namespace penny {
 PK_HD size_t oneshot_flag_scratch_bytes(size_t n, int elem_size, int world) {
   return 2 * (size_t)world * vecs_for(n, elem_size) * 16;
 }
-// both halves of: [src world][V] pairs of 16-byte lines
+// both halves of: [src world][V rounded up to 32] pairs of 16-byte lines
 PK_HD size_t oneshot_ll_scratch_bytes(size_t n, int elem_size, int world) {
-  return 4 * (size_t)world * vecs_for(n, elem_size) * 16;
+  return 4 * (size_t)world * ((vecs_for(n, elem_size) + 31) / 32 * 32) * 16;
+}
+// Byte offset of line j (0 or 1) of vector v sent by rank s.  32 consecutive vectors share two
+// 512-byte rows (all their lines 0, then all their lines 1), so the store instruction of a warp
+// whose lanes hold consecutive vectors writes 512 contiguous bytes - four whole 128-byte lines on
+// the wire instead of 32 half-written sectors.
+PK_HD size_t ll_line_off(size_t vpad, int s, size_t v, int j) {
+  return (((size_t)s * vpad + (v & ~(size_t)31)) * 2 + (size_t)j * 32 + (v & 31)) * 16;
 }
 
 template <typename T, int NG>
@@ -109,6 +116,7 @@ struct OneShotLL {
     const T* in = reinterpret_cast<const T*>(a.in);
     T* out = reinterpret_cast<T*>(a.out);
     const size_t V = ceil_div(a.n, E);
+    const size_t vpad = (V + 31) / 32 * 32;
     const size_t base = scratch_half(a.scratch_off, a.scratch_bytes, seq);
     const uint32_t e = ll_flag(seq);
     const size_t stride = (size_t)b.nblocks * b.nthreads;
@@ -123,9 +131,8 @@ struct OneShotLL {
 #pragma unroll
         for (int d = 1; d < NG; ++d) {
           const int p = (rank + d) % NG;
-          char* dst = c.heap[p] + base + ((size_t)rank * V + v) * 32;
-          st16_volatile(dst, l0);
-          st16_volatile(dst + 16, l1);
+          st16_volatile(c.heap[p] + base + ll_line_off(vpad, rank, v, 0), l0);
+          st16_volatile(c.heap[p] + base + ll_line_off(vpad, rank, v, 1), l1);
         }
       }
     }
@@ -141,10 +148,10 @@ struct OneShotLL {
           if (s == rank) {
             x = load_user_vec<T>(in, v, a.n);
           } else {
-            const char* src = c.heap[rank] + base + ((size_t)s * V + v) * 32;
+            const char* src = c.heap[rank] + base;
             V16 l0, l1;
-            ok = ok && ll_wait_line(src, e, l0, c, s, b.bid);
-            ok = ok && ll_wait_line(src + 16, e, l1, c, s, b.bid);
+            ok = ok && ll_wait_line(src + ll_line_off(vpad, s, v, 0), e, l0, c, s, b.bid);
+            ok = ok && ll_wait_line(src + ll_line_off(vpad, s, v, 1), e, l1, c, s, b.bid);
             x.w[0] = l0.w[0]; x.w[1] = l0.w[2]; x.w[2] = l1.w[0]; x.w[3] = l1.w[2];
           }
           unpack_add<T>(x, acc);

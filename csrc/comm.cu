@@ -112,7 +112,7 @@ Communicator::Region& Communicator::ensure(Region& r, size_t need, const char* w
 }
 
 LaunchCfg Communicator::cfg_for(size_t vecs, const Tuning& t, cudaStream_t s, int max_blocks,
-                                int multiple) const {
+                                int multiple, int vecs_per_thread) const {
   LaunchCfg cfg;
   cfg.threads = t.threads > 0 ? t.threads : 512;
   cfg.stream = s;
@@ -124,7 +124,7 @@ LaunchCfg Communicator::cfg_for(size_t vecs, const Tuning& t, cudaStream_t s, in
   max_blocks = std::min(max_blocks, kMaxBlocks);
   int blocks = t.blocks;
   if (blocks <= 0) {
-    size_t per_block = (size_t)cfg.threads * 4;
+    size_t per_block = (size_t)cfg.threads * vecs_per_thread;
     blocks = (int)std::min<size_t>((size_t)max_blocks, std::max<size_t>(1, ceil_div(vecs, per_block)));
   }
   blocks = std::min(blocks, max_blocks);
@@ -239,7 +239,8 @@ void Communicator::run_all_reduce_once(int algo, int dtype, const void* const* i
   switch (algo) {
     case ALGO_ONESHOT: {
       set_scratch(ensure(scratch_, oneshot_flag_scratch_bytes(n, es, world_), "one-shot"));
-      rc = launch_all_reduce_oneshot(dtype, false, ctx_, a, cfg_for(V, t, stream, 64, 1));
+      // latency-bound: one vector per thread while the blocks last
+      rc = launch_all_reduce_oneshot(dtype, false, ctx_, a, cfg_for(V, t, stream, 64, 1, 1));
       break;
     }
     case ALGO_ONESHOT_LL: {
@@ -323,7 +324,7 @@ void Communicator::run_all_reduce_once(int algo, int dtype, const void* const* i
         }
       }
       rc = launch_all_reduce_nvls(dtype, oneshot, ctx_, a,
-                                  cfg_for(oneshot ? V : ceil_div(V, world_), t, stream, 64, 1));
+                                  cfg_for(oneshot ? V : ceil_div(V, world_), t, stream, 64, 1, oneshot ? 1 : 4));
       if (rc == cudaSuccess && !oneshot && !out_heap)
         ckrt(cudaMemcpyAsync(out[0], local_ptr(stage_out_.off), n * es, cudaMemcpyDeviceToDevice,
                              stream), "stage out");

@@ -144,7 +144,8 @@ class Communicator {
   };
   Region& ensure(Region& r, size_t need, const char* what);
   void init_ctx(const CommOptions& opt);
-  LaunchCfg cfg_for(size_t vecs, const Tuning& t, cudaStream_t s, int max_blocks, int multiple) const;
+  LaunchCfg cfg_for(size_t vecs, const Tuning& t, cudaStream_t s, int max_blocks, int multiple,
+                    int vecs_per_thread = 4) const;
   void run_all_reduce_once(int algo, int dtype, const void* const* in, void* const* out, size_t n,
                            const Tuning& t, cudaStream_t stream);
 

@@ -7,6 +7,10 @@ except where DRAM figures need inputs larger than L2).
     python extra/profile_kernels.py attention   # decode attention, batch 64 x 8 KV heads x 2048
     python extra/profile_kernels.py fused       # all-reduce+residual+RMSNorm, 8 emulated ranks
     python extra/profile_kernels.py allreduce   # two-shot / LL all-reduce, 8 emulated ranks
+    python extra/profile_kernels.py attention_fused   # one-launch decode attention (RoPE + KV append + split merge)
+    python extra/profile_kernels.py gemm_decode       # decode-batch GEMM: a wide matrix (no cluster) and a narrow one (cluster split-K)
+    python extra/profile_kernels.py fused_twoshot     # flag-in-data two-shot all-reduce+RMSNorm, 8 emulated ranks
+    python extra/profile_kernels.py collectives       # reduce-scatter / all-gather / all-to-all (push and pipelined), 8 emulated ranks
 
 Each prints the CUDA-event time per launch so that the same command line can be
 run plainly first and under `ncu --clock-control none -k regex:<kernel> -c <n>`
@@ -65,6 +69,56 @@ def main():
         t = timed(lambda: ops.decode_attention(qkv, kc, vc, pos, out, ws, Hq, Hkv, splits, 1 / math.sqrt(D)))
         gb = B * Hkv * (L + 1) * D * 2 * 2 / 1e9
         print(f"decode_attention B={B} Hkv={Hkv} L={L}: {t:.1f} us, {gb / t * 1e6:.0f} GB/s of K+V")
+    elif what == "attention_fused":
+        # the shard one rank of a TP-8 group sees (4 splits: 256 CTAs) and the TP-1 shape (no split)
+        for Hq, Hkv, splits in ((4, 1, 4), (32, 8, 1)):
+            B, D, L = 64, 128, 2048
+            qkv = torch.randn(B, (Hq + 2 * Hkv) * D, device="cuda").bfloat16()
+            kc = torch.randn(B, Hkv, L + 16, D, device="cuda").bfloat16()
+            vc = torch.randn(B, Hkv, L + 16, D, device="cuda").bfloat16()
+            pos = torch.full((B,), L, dtype=torch.int32, device="cuda")
+            out = torch.empty(B, Hq * D, device="cuda", dtype=torch.bfloat16)
+            ws = torch.zeros(ops.decode_attn_fused_workspace_bytes(B, Hq, Hkv, splits), dtype=torch.uint8, device="cuda")
+            t = timed(lambda: ops.decode_attention_fused(qkv, kc, vc, pos, out, ws, Hq, Hkv, splits, 1 / math.sqrt(D),
+                                                         500000.0, False))
+            gb = B * Hkv * (L + 1) * D * 2 * 2 / 1e9
+            print(f"decode_attention_fused B={B} Hq={Hq} Hkv={Hkv} L={L} splits={splits}: {t:.1f} us, "
+                  f"{gb / t * 1e6:.0f} GB/s of K+V (L2-warm when the cache fits)")
+    elif what == "gemm_decode":
+        B = 64
+        x4096 = torch.randn(B, 4096, device="cuda").bfloat16() * 0.1
+        for name, N, K in (("gate_up TP1", 28672, 4096), ("qkv TP8", 768, 4096), ("down TP8", 4096, 1792)):
+            x = x4096 if K == 4096 else torch.randn(B, K, device="cuda").bfloat16() * 0.1
+            w = torch.randn(N, K, device="cuda").bfloat16() * 0.05
+            out = torch.empty(B, N, device="cuda", dtype=torch.bfloat16)
+            t = timed(lambda: ops.gemm_decode(x, w, out, False, 0, False))
+            assert ops.gemm_error() == 0
+            print(f"gemm_decode {name} {N}x{K} batch {B}, cluster {ops.gemm_decode_splits(B, N, K)}: {t:.1f} us, "
+                  f"{N * K * 2 / t / 1e3:.0f} GB/s of W (back-to-back launches: W of {N * K * 2 >> 20} MiB "
+                  f"{'stays in' if N * K * 2 < (100 << 20) else 'exceeds'} L2)")
+    elif what in ("fused_twoshot", "collectives"):
+        from penny_b200.parallel.comm import Communicator
+        comm = Communicator.emulated(8, heap_bytes=256 << 20)
+        if what == "fused_twoshot":
+            rows, hidden = 64, 4096
+            x = [torch.randn(rows, hidden, device="cuda").bfloat16() for _ in range(8)]
+            r = [torch.randn(rows, hidden, device="cuda").bfloat16() for _ in range(8)]
+            w = torch.ones(hidden, device="cuda", dtype=torch.bfloat16)
+            o = [torch.empty_like(t) for t in x]
+            t = timed(lambda: comm.fused_all_reduce_rmsnorm(x, w, residual=r, out=o, proto="ll_twoshot"))
+            print(f"fused all-reduce+rmsnorm (ll_twoshot) rows={rows}, 8 emulated ranks on one GPU: {t:.1f} us")
+        else:
+            n = 1 << 22  # 8 MiB per rank
+            x = [torch.randn(n, device="cuda").bfloat16() for _ in range(8)]
+            for name, fn in (("reduce_scatter push", lambda: comm.reduce_scatter(x, algo="push")),
+                             ("reduce_scatter pipelined", lambda: comm.reduce_scatter(x, algo="pipelined")),
+                             ("all_gather push", lambda: comm.all_gather(x, algo="push")),
+                             ("all_to_all push", lambda: comm.all_to_all(x, algo="push")),
+                             ("all_to_all pipelined", lambda: comm.all_to_all(x, algo="pipelined"))):
+                t = timed(fn)
+                print(f"{name} {n * 2 >> 20} MiB per rank bf16, 8 emulated ranks on one GPU: {t:.1f} us")
+        comm.check()
+        comm.close()
     elif what in ("fused", "allreduce"):
         from penny_b200.parallel.comm import Communicator
         comm = Communicator.emulated(8, heap_bytes=256 << 20)
