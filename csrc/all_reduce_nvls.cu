@@ -7,15 +7,23 @@
 //
 //   NvlsTwoShot   rank r reduces chunk r with ld_reduce and multicasts the
 //                 result: each GPU's links carry S/N + S bytes instead of the
-//                 2 * S * (N-1)/N of any peer-to-peer algorithm.
-//   NvlsOneShot   every rank ld_reduces the whole buffer into its own output
-//                 (which may be ordinary memory): lowest latency for small S.
+//                 2 * S * (N-1)/N of any peer-to-peer algorithm.  Input and output
+//                 in the heap at the same offset on every rank.
+//   NvlsTwoShotStaged   the same for tensors anywhere in device memory, in one
+//                 kernel: stage the input into this call's scratch half, barrier,
+//                 reduce + multicast into the other part of the half, barrier, copy
+//                 out.  Block b stages, reduces and copies the same positions of
+//                 every rank's chunk, so the barriers stay block-local.
+//   NvlsOneShot   stage the input into this call's scratch half, ONE barrier, then
+//                 every rank ld_reduces the whole buffer into its own output.  No
+//                 second barrier: the next call uses the other half, and a rank can
+//                 only reach the call after that once every peer has left this one.
 //   NvlsReduceScatter / NvlsAllGather   the two halves on their own.
 //
-// Input (and for two-shot / all-gather the output) must live in the heap at the
-// same offset on every rank.  Both barriers are needed: the first says "my input
-// is complete", the second "the switch has finished reading my input and my
-// writes have landed", so a buffer may be reused right after the call.
+// Unless staged, the input (and for two-shot / all-gather the output) must live in
+// the heap at the same offset on every rank, and both barriers are needed: the first
+// says "my input is complete", the second "the switch has finished reading my input
+// and my writes have landed", so a buffer may be reused right after the call.
 // The reference has no NVLS path (it predates it: NVSHMEM puts + signals only).
 #include "algos.h"
 #include "launch.cuh"
@@ -87,22 +95,81 @@ struct NvlsTwoShot {
   }
 };
 
+// scratch: both halves of [V] staged vectors
+PK_HD size_t nvls_oneshot_scratch_bytes(size_t n, int elem_size) { return 2 * vecs_for(n, elem_size) * 16; }
+// scratch: both halves of ([V] staged input + [V] reduced output)
+PK_HD size_t nvls_staged_scratch_bytes(size_t n, int elem_size) { return 4 * vecs_for(n, elem_size) * 16; }
+
 template <typename T>
 struct NvlsOneShot {
   static __device__ void body(const CommCtx& c, int rank, const CollArgs& a, const Blk& b, u64 seq,
                               int& s_abort) {
     constexpr size_t E = 16 / sizeof(T);
+    const T* in = reinterpret_cast<const T*>(a.in);
     T* out = reinterpret_cast<T*>(a.out);
     const size_t V = ceil_div(a.n, E);
+    const size_t base = scratch_half(a.scratch_off, a.scratch_bytes, seq);
     const size_t stride = (size_t)b.nblocks * b.nthreads;
+    const size_t first = (size_t)b.bid * b.nthreads + threadIdx.x;
+    for (size_t v = first; v < V; v += stride) st16(c.heap[rank] + base + v * 16, load_user_vec<T>(in, v, a.n));
     PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 1), s_abort);
     if (s_abort) return;
-    for (size_t v = (size_t)b.bid * b.nthreads + threadIdx.x; v < V; v += stride)
-      store_user_vec<T>(out, v, a.n, multimem_ld_reduce<T>(c.mc + a.in_heap_off + v * 16));
-    PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 2), s_abort);
+    for (size_t v0 = first; v0 < V; v0 += kBatch * stride) {
+      V16 r[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u)
+        if (v0 + u * stride < V) r[u] = multimem_ld_reduce<T>(c.mc + base + (v0 + u * stride) * 16);
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u)
+        if (v0 + u * stride < V) store_user_vec<T>(out, v0 + u * stride, a.n, r[u]);
+    }
   }
   static __device__ void run(const CommCtx& c, int rank, const CollArgs& a, const Blk& b) {
     run_collective<NvlsOneShot<T>, CollArgs>(c, rank, a, b);
+  }
+};
+
+template <typename T>
+struct NvlsTwoShotStaged {
+  static __device__ void body(const CommCtx& c, int rank, const CollArgs& a, const Blk& b, u64 seq,
+                              int& s_abort) {
+    constexpr size_t E = 16 / sizeof(T);
+    const T* in = reinterpret_cast<const T*>(a.in);
+    T* out = reinterpret_cast<T*>(a.out);
+    const size_t V = ceil_div(a.n, E);
+    const size_t in_base = scratch_half(a.scratch_off, a.scratch_bytes, seq);
+    const size_t out_base = in_base + V * 16;
+    const size_t stride = (size_t)b.nblocks * b.nthreads;
+    const size_t first = (size_t)b.bid * b.nthreads + threadIdx.x;
+    // position j of EVERY rank's chunk belongs to the same (block, thread) on every rank
+    for (int s = 0; s < c.world; ++s) {
+      const Span sp = split_span(V, c.world, s);
+      for (size_t j = first; j < sp.end - sp.begin; j += stride)
+        st16(c.heap[rank] + in_base + (sp.begin + j) * 16, load_user_vec<T>(in, sp.begin + j, a.n));
+    }
+    PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 1), s_abort);
+    if (s_abort) return;
+    const Span mine = split_span(V, c.world, rank);
+    const size_t len = mine.end - mine.begin;
+    for (size_t j0 = first; j0 < len; j0 += kBatch * stride) {
+      V16 r[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u)
+        if (j0 + u * stride < len) r[u] = multimem_ld_reduce<T>(c.mc + in_base + (mine.begin + j0 + u * stride) * 16);
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u)
+        if (j0 + u * stride < len) multimem_st(c.mc + out_base + (mine.begin + j0 + u * stride) * 16, r[u]);
+    }
+    PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 2), s_abort);
+    if (s_abort) return;
+    for (int s = 0; s < c.world; ++s) {
+      const Span sp = split_span(V, c.world, s);
+      for (size_t j = first; j < sp.end - sp.begin; j += stride)
+        store_user_vec<T>(out, sp.begin + j, a.n, ld16(c.heap[rank] + out_base + (sp.begin + j) * 16));
+    }
+  }
+  static __device__ void run(const CommCtx& c, int rank, const CollArgs& a, const Blk& b) {
+    run_collective<NvlsTwoShotStaged<T>, CollArgs>(c, rank, a, b);
   }
 };
 
@@ -153,14 +220,19 @@ static bool nvls_ok(const CommCtx& c, const LaunchCfg& cfg) {
   return c.mc != nullptr && cfg.emu_world <= 0;
 }
 
-cudaError_t launch_all_reduce_nvls(int dtype, bool oneshot, const CommCtx& c, const CollArgs* a,
+size_t nvls_oneshot_scratch(size_t n, int elem_size) { return nvls_oneshot_scratch_bytes(n, elem_size); }
+size_t nvls_staged_scratch(size_t n, int elem_size) { return nvls_staged_scratch_bytes(n, elem_size); }
+
+cudaError_t launch_all_reduce_nvls(int dtype, int kind, const CommCtx& c, const CollArgs* a,
                                    const LaunchCfg& cfg) {
-  if (!nvls_ok(c, cfg) || a[0].in_heap_off == kNotInHeap) return cudaErrorNotSupported;
-  if (!oneshot && a[0].out_heap_off == kNotInHeap) return cudaErrorNotSupported;
+  if (!nvls_ok(c, cfg)) return cudaErrorNotSupported;
+  if (kind == NVLS_TWOSHOT && (a[0].in_heap_off == kNotInHeap || a[0].out_heap_off == kNotInHeap))
+    return cudaErrorNotSupported;
   cudaError_t rc = cudaErrorInvalidValue;
   PENNY_DISPATCH_DTYPE(dtype, T, {
-    rc = oneshot ? launch_body<NvlsOneShot<T>, CollArgs>(c, a, cfg)
-                 : launch_body<NvlsTwoShot<T>, CollArgs>(c, a, cfg);
+    rc = kind == NVLS_ONESHOT   ? launch_body<NvlsOneShot<T>, CollArgs>(c, a, cfg)
+         : kind == NVLS_STAGED ? launch_body<NvlsTwoShotStaged<T>, CollArgs>(c, a, cfg)
+                               : launch_body<NvlsTwoShot<T>, CollArgs>(c, a, cfg);
   });
   return rc;
 }

@@ -23,6 +23,9 @@ void ckrt(cudaError_t r, const char* what) {
   }
 }
 constexpr size_t kScratchCap = (size_t)512 << 20;  // a single call never asks for more
+// Switch all-reduce of tensors outside the heap: up to this size the staging copies run inside the
+// kernel (one launch instead of three); above it the copy engines' rate wins.
+constexpr size_t kNvlsStageInKernelBytes = (size_t)1 << 20;
 }  // namespace
 
 Communicator::Communicator(const std::string& uid, int rank, int world, const CommOptions& opt)
@@ -188,8 +191,8 @@ void Communicator::all_reduce(int algo, int dtype, const void* const* in, void* 
     case ALGO_ONESHOT: per_elem_scratch = 2 * (size_t)world_ * es; break;
     case ALGO_ONESHOT_LL: per_elem_scratch = 4 * (size_t)world_ * es; break;
     case ALGO_TREE: per_elem_scratch = 2 * (size_t)(2 + t.nnodes) * es; break;
-    case ALGO_NVLS:
-    case ALGO_NVLS_ONESHOT: per_elem_scratch = es; break;  // staging at most
+    case ALGO_NVLS: per_elem_scratch = es; break;  // staging at most (the in-kernel variant is small by construction)
+    case ALGO_NVLS_ONESHOT: per_elem_scratch = 2 * (size_t)es; break;
     default: per_elem_scratch = 4 * (size_t)es; break;
   }
   size_t budget = std::min(kScratchCap, std::max<size_t>(heap_free_bytes() / 2, (size_t)1 << 20));
@@ -292,40 +295,44 @@ void Communicator::run_all_reduce_once(int algo, int dtype, const void* const* i
       rc = launch_all_reduce_tree(dtype, ctx_, a, cfg_for(ceil_div(V, gpn), t, stream, 96, gpn));
       break;
     }
-    case ALGO_NVLS:
     case ALGO_NVLS_ONESHOT: {
-      const bool oneshot = algo == ALGO_NVLS_ONESHOT;
+      // stages its input inside the kernel: any memory, in place or not
+      set_scratch(ensure(scratch_, nvls_oneshot_scratch(n, es), "NVLS one-shot"));
+      rc = launch_all_reduce_nvls(dtype, NVLS_ONESHOT, ctx_, a, cfg_for(V, t, stream, 64, 1, 1));
+      break;
+    }
+    case ALGO_NVLS: {
       const size_t bytes = V * 16;
-      // the switch reads the heap: stage tensors that live elsewhere
-      bool in_heap = a[0].in_heap_off != kNotInHeap && t.symmetric_in;
-      size_t out_off = heap_offset_of(out[0], 0);
-      bool out_heap = out_off != kNotInHeap && t.symmetric_out;
-      // One-shot: every rank reads all inputs through the switch while the others
-      // may already be storing their results, so an output that overlaps the
-      // symmetric input would be overwritten before a peer has reduced it.  Such a
-      // call reads from a staged copy of the input instead.
-      if (oneshot && in_heap) {
-        const char* ib = (const char*)in[0];
-        const char* ob = (const char*)out[0];
-        if (ob < ib + n * es && ib < ob + n * es) in_heap = false;
+      const bool in_heap = a[0].in_heap_off != kNotInHeap && t.symmetric_in;
+      const size_t out_off = heap_offset_of(out[0], 0);
+      const bool out_heap = out_off != kNotInHeap && t.symmetric_out;
+      if (in_heap && out_heap) {
+        a[0].out_heap_off = out_off;
+        rc = launch_all_reduce_nvls(dtype, NVLS_TWOSHOT, ctx_, a, cfg_for(ceil_div(V, world_), t, stream, 64, 1));
+        break;
       }
+      if (bytes <= kNvlsStageInKernelBytes) {
+        // tensors outside the heap, small enough that two extra copy launches would cost more than
+        // copying inside the kernel: one launch, staged through this call's scratch half
+        set_scratch(ensure(scratch_, nvls_staged_scratch(n, es), "NVLS staged"));
+        rc = launch_all_reduce_nvls(dtype, NVLS_STAGED, ctx_, a, cfg_for(ceil_div(V, world_), t, stream, 64, 1, 2));
+        break;
+      }
+      // large: the copy engines' rate matters more than two launches
       if (!in_heap) {
         ensure(stage_in_, bytes, "NVLS input staging");
         ckrt(cudaMemcpyAsync(local_ptr(stage_in_.off), in[0], n * es, cudaMemcpyDeviceToDevice,
                              stream), "stage in");
         a[0].in_heap_off = stage_in_.off;
       }
-      if (!oneshot) {
-        if (!out_heap) {
-          ensure(stage_out_, bytes, "NVLS output staging");
-          a[0].out_heap_off = stage_out_.off;
-        } else {
-          a[0].out_heap_off = out_off;
-        }
+      if (!out_heap) {
+        ensure(stage_out_, bytes, "NVLS output staging");
+        a[0].out_heap_off = stage_out_.off;
+      } else {
+        a[0].out_heap_off = out_off;
       }
-      rc = launch_all_reduce_nvls(dtype, oneshot, ctx_, a,
-                                  cfg_for(oneshot ? V : ceil_div(V, world_), t, stream, 64, 1, oneshot ? 1 : 4));
-      if (rc == cudaSuccess && !oneshot && !out_heap)
+      rc = launch_all_reduce_nvls(dtype, NVLS_TWOSHOT, ctx_, a, cfg_for(ceil_div(V, world_), t, stream, 64, 1));
+      if (rc == cudaSuccess && !out_heap)
         ckrt(cudaMemcpyAsync(out[0], local_ptr(stage_out_.off), n * es, cudaMemcpyDeviceToDevice,
                              stream), "stage out");
       break;

@@ -2,7 +2,8 @@
 // kernel, by its launcher and (through the host simulator library) by the CPU
 // tests.
 //
-//   out[B, N] = x[B, K] W[N, K]^T for a decode batch (B <= 128).
+//   out[B, N] = x[B, K] W[N, K]^T for a decode batch (one slab of B <= 128 rows; larger batches run
+//   their slabs as grid z of the same launch, so the slabs of a weight tile read it from L2 together).
 //   * one CTA per (weight tile of 128 rows, K range); the `splits` CTAs of a tile
 //     form one thread-block cluster and reduce their fp32 partials through
 //     distributed shared memory: no global workspace, no counters, no fix-up pass;
@@ -25,6 +26,7 @@ namespace penny {
 namespace sm100 {
 
 constexpr int kDecodeMaxSplits = 8;  // portable cluster size
+constexpr int kDecodeMaxBatch = 1024;  // rows of x per launch
 
 PENNY_PLAN_HD int decode_kb_begin(int num_kb, int splits, int r) {
   return (int)((long long)num_kb * r / splits);

@@ -43,7 +43,7 @@ void bind_gemm(py::module_& m) {
         (int)out.stride(0), (int)block_n, penny_gemm_error_word(), at::cuda::getCurrentCUDAStream().stream());
     TORCH_CHECK(rc == cudaSuccess, "gemm_bf16: ", cudaGetErrorString(rc));
   }, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("block_n") = 0);
-  // Decode-batch linear: out[B, N] = x[B, K] @ w[N, K]^T for B <= 128.  One CTA per (weight tile, K
+  // Decode-batch linear: out[B, N] = x[B, K] @ w[N, K]^T for B <= 1024 (slabs of 128 rows in one launch).  One CTA per (weight tile, K
   // range); the K ranges of a tile are reduced inside a thread-block cluster through distributed shared
   // memory.  pdl: may start (and load w) while the previous kernel on the stream still runs, so w must not
   // be written by that kernel.  silu_pairs: w's rows are blocks of 64 gate + 64 up rows and out is
@@ -56,7 +56,8 @@ void bind_gemm(py::module_& m) {
     TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm_decode: 2-D tensors");
     TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1, "gemm_decode: rows must be contiguous");
     const int64_t B = x.size(0), K = x.size(1), N = w.size(0);
-    TORCH_CHECK(B >= 1 && B <= 128, "gemm_decode: 1 <= rows of x <= 128 (use gemm_bf16 beyond)");
+    TORCH_CHECK(B >= 1 && B <= penny::sm100::kDecodeMaxBatch, "gemm_decode: 1 <= rows of x <= 1024 (use gemm_bf16 beyond)");
+    TORCH_CHECK(!push.has_value() || B <= 128, "gemm_decode: push needs rows of x <= 128");
     TORCH_CHECK(w.size(1) == K && out.size(0) == B && out.size(1) == (silu_pairs ? N / 2 : N),
                 "gemm_decode: shape mismatch");
     TORCH_CHECK(splits >= 0 && splits <= 8, "gemm_decode: 0 <= splits <= 8");

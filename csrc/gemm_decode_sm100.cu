@@ -164,7 +164,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   pdl_launch_dependents();
-  const int cta_lin = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+  const int cta_lin = (int)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x);
   auto stamp = [&](int point) {
     if (a.stamps && cta_lin < kStampCtas) g_dec_stamps[cta_lin * kStampPoints + point] = gtime_ns();
   };
@@ -173,6 +173,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t crank = S > 1 ? cluster_ctarank() : 0u;
   const int tile = (int)blockIdx.y;
+  const int row0 = (int)blockIdx.z * BT;  // batch slab of this CTA (batches above BT rows: one slab per grid z)
   const int kb0 = decode_kb_begin(a.num_kb, S, (int)crank), kb1 = decode_kb_begin(a.num_kb, S, (int)crank + 1);
   const int nkb = kb1 - kb0;
   const int sl = decode_slice(BT, S);
@@ -232,7 +233,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       pdl_wait();
       stamp(2);  // predecessor complete
       for (int i = 0; i < pre; ++i)
-        tma_load_2d(tiles + (size_t)i * Cfg::kStageBytes + Cfg::kWBytes, &map_x, &full[i], kb_at(i) * kBlockK, 0);
+        tma_load_2d(tiles + (size_t)i * Cfg::kStageBytes + Cfg::kWBytes, &map_x, &full[i], kb_at(i) * kBlockK, row0);
       int stage = pre == stages ? 0 : pre;
       uint32_t phase = pre == stages ? 1u : 0u;
       bool ok = true;
@@ -244,7 +245,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         unsigned char* sw = tiles + (size_t)stage * Cfg::kStageBytes;
         mbar_expect_tx(&full[stage], Cfg::kStageBytes);
         tma_load_2d(sw, &map_w, &full[stage], kb_at(i) * kBlockK, tile * kBlockM);
-        tma_load_2d(sw + Cfg::kWBytes, &map_x, &full[stage], kb_at(i) * kBlockK, 0);
+        tma_load_2d(sw + Cfg::kWBytes, &map_x, &full[stage], kb_at(i) * kBlockK, row0);
         if (pf_next < nkb && pf_next < i + a.l2_ahead) {
           tma_prefetch_l2_2d(&map_w, kb_at(pf_next) * kBlockK, tile * kBlockM);
           ++pf_next;
@@ -359,7 +360,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       // ---- my slice: add the peers' partials in rank order, apply the epilogue, store.
       // A work item is 8 consecutive rows (output columns) of one batch column; a warp takes the
       // items of its own row quarter (gate/up: gate rows 16 q .. 16 q + 15 and their up rows).
-      const int lo = (int)crank * sl, hi = min(min(BT, lo + sl), a.B);
+      const int lo = (int)crank * sl, hi = min(min(BT, lo + sl), a.B - row0);
       const int groups = silu ? 2 : 4;  // row groups of 8 per column in this warp's share
       const int n_out = silu ? a.N / 2 : a.N;
       const int n_tile0 = tile * (silu ? kBlockM / 2 : kBlockM);
@@ -398,7 +399,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           for (int k = 0; k < 8; ++k) v[k] = v[k] / (1.f + __expf(-v[k])) * u[k];
         }
         const int n0 = n_tile0 + g * 8;
-        __nv_bfloat16* dst = a.out + (size_t)j * a.ldo + n0;
+        __nv_bfloat16* dst = a.out + (size_t)(row0 + j) * a.ldo + n0;
         if (vec_ok && n0 + 8 <= n_out) {
           uint4 o;
           o.x = pack_bf16x2(__float_as_uint(v[0]), __float_as_uint(v[1]));
@@ -503,7 +504,8 @@ cudaError_t launch_decode_bt(const void* x, const void* w, void* out, int B, int
   a.K = K;
   a.num_kb = (K + kBlockK - 1) / kBlockK;
   const int tiles = (N + kBlockM - 1) / kBlockM;
-  if (splits <= 0) splits = decode_choose_splits(tiles, a.num_kb, decode_capacity<BT>(sms));
+  const int slabs = (B + BT - 1) / BT;  // > 1 only with BT = 128: the slabs of a tile run side by side and share W in L2
+  if (splits <= 0) splits = decode_choose_splits(tiles * slabs, a.num_kb, decode_capacity<BT>(sms));
   splits = std::max(1, std::min(splits, std::min(kDecodeMaxSplits, a.num_kb)));
   a.splits = splits;
   a.epi = epi;
@@ -533,7 +535,7 @@ cudaError_t launch_decode_bt(const void* x, const void* w, void* out, int B, int
   a.stamps = env_stamps;
   rc = kernel_setup(reinterpret_cast<const void*>(gemm_decode_kernel<BT>), 227 << 10).rc;
   if (rc != cudaSuccess) return rc;
-  return launch_kernel_ex(gemm_decode_kernel<BT>, dim3((unsigned)splits, (unsigned)tiles, 1), dim3(kDecThreads), smem,
+  return launch_kernel_ex(gemm_decode_kernel<BT>, dim3((unsigned)splits, (unsigned)tiles, (unsigned)slabs), dim3(kDecThreads), smem,
                           stream, pdl, splits, mw, mx, a, error_word);
 }
 
@@ -542,8 +544,9 @@ cudaError_t launch_decode_bt(const void* x, const void* w, void* out, int B, int
 cudaError_t launch_gemm_decode(const void* x, const void* w, void* out, int B, int N, int K, int ldx, int ldw,
                                int ldo, int epi, int splits, bool pdl, long long l2_budget_bytes,
                                int smem_kb, const DecodePush* push, uint32_t* error_word, cudaStream_t stream) {
-  if (B <= 0 || B > 128 || N <= 0 || K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0)
+  if (B <= 0 || B > kDecodeMaxBatch || N <= 0 || K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0)
     return cudaErrorInvalidValue;
+  if (push != nullptr && B > 128) return cudaErrorInvalidValue;  // the owners' receive lines cover one slab
   if (epi != DECODE_EPI_PLAIN && epi != DECODE_EPI_SILU_PAIRS) return cudaErrorInvalidValue;
   if (epi == DECODE_EPI_SILU_PAIRS && N % kBlockM != 0) return cudaErrorInvalidValue;
   if ((N + kBlockM - 1) / kBlockM > 65535) return cudaErrorInvalidValue;
@@ -584,7 +587,7 @@ int gemm_decode_splits(int B, int N, int K) {
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   (void)cudaGetLastError();
   if (sms <= 0) sms = 148;
-  const int num_kb = (K + kBlockK - 1) / kBlockK, tiles = (N + kBlockM - 1) / kBlockM;
+  const int num_kb = (K + kBlockK - 1) / kBlockK, tiles = (N + kBlockM - 1) / kBlockM * ((std::max(B, 1) + 127) / 128);
   const int* cap = B <= 32 ? decode_capacity<32>(sms) : (B <= 64 ? decode_capacity<64>(sms) : decode_capacity<128>(sms));
   return decode_choose_splits(tiles, num_kb, cap);
 }

@@ -3,6 +3,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "decode_gemm_plan.h"
+
 namespace penny {
 namespace sm100 {
 
@@ -28,7 +30,7 @@ struct DecodePush {
 };
 
 // out[B, N] = x[B, K] * W[N, K]^T, bf16, row-major with leading dimensions ldx /
-// ldw / ldo (elements); 1 <= B <= 128; K, ldx, ldw multiples of 8; x, w 16-byte aligned.
+// ldw / ldo (elements); 1 <= B <= kDecodeMaxBatch (above 128 rows the batch is cut into slabs of 128, all in this one launch; push: B <= 128); K, ldx, ldw multiples of 8; x, w 16-byte aligned.
 //   splits          CTAs per weight tile (cluster size along K), 0 = choose
 //   pdl             launch with programmatic stream serialization: the kernel may
 //                   start, and load W, while the previous kernel on the stream is

@@ -273,10 +273,11 @@ class LlamaTPDecoder:
             ops.add_rmsnorm(part, self.residual, weight, self.x, self.residual, self.cfg.eps)
 
     def _linear(self, x, w, out, silu_pairs=False, smem_kb=0, push=None):
-        """out = x @ w^T on this library's decode GEMM, 128 rows of x per launch."""
+        """out = x @ w^T on this library's decode GEMM: one launch (batches above 128 rows run as
+        slabs of 128 rows inside it, 1024 rows per launch at most)."""
         B = x.shape[0]
-        for r in range(0, B, 128):
-            ops.gemm_decode(x[r:r + 128], w, out[r:r + 128], silu_pairs, 0, self.pdl, -1, smem_kb, push)
+        for r in range(0, B, 1024):
+            ops.gemm_decode(x[r:r + 1024], w, out[r:r + 1024], silu_pairs, 0, self.pdl, -1, smem_kb, push)
 
     def _step_impl(self):
         cfg = self.cfg

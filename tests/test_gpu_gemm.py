@@ -172,6 +172,32 @@ def test_gemm_decode_matches_fp32(shape, splits):
         torch.testing.assert_close(out.float(), ref(x, w), atol=2e-2 * (K ** 0.5) * 0.25 + 1e-2, rtol=1.6e-2)
 
 
+@pytest.mark.parametrize("splits", [0, 1, 4])
+@pytest.mark.parametrize("shape", [(256, 768, 4096), (200, 1000, 512), (129, 4096, 1792), (1024, 256, 128)])
+def test_gemm_decode_batch_slabs(shape, splits):
+    """Batches above 128 rows: slabs of 128 rows as grid z of one launch (the last one ragged);
+    plain and gate/up epilogues."""
+    from penny_b200._ext import ops
+    B, N, K = shape
+    if splits > K // 64:
+        pytest.skip("more K ranges than K steps")
+    g = torch.Generator(device="cuda").manual_seed(B + N + K)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.5).bfloat16()
+    x = (torch.randn(B, K, device="cuda", generator=g) * 0.5).bfloat16()
+    out = torch.full((B, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.gemm_decode(x, w, out, False, splits)
+    assert ops.gemm_error() == 0
+    torch.testing.assert_close(out.float(), ref(x, w), atol=2e-2 * (K ** 0.5) * 0.25 + 1e-2, rtol=1.6e-2)
+    if N % 128 == 0:
+        w2 = (w.float() * 0.1).bfloat16()
+        out2 = torch.full((B, N // 2), float("nan"), device="cuda", dtype=torch.bfloat16)
+        ops.gemm_decode(x, w2, out2, True, splits)
+        assert ops.gemm_error() == 0
+        y = (x.float() @ w2.float().t()).view(B, N // 128, 2, 64)
+        want = (torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]).reshape(B, N // 2)
+        torch.testing.assert_close(out2.float(), want, atol=5e-2, rtol=3e-2)
+
+
 @pytest.mark.parametrize("splits", [0, 1, 4, 7])
 @pytest.mark.parametrize("shape", [(64, 3584, 4096), (5, 256, 320), (128, 1792, 1024), (20, 1792, 512)])
 def test_gemm_decode_fused_silu_mul(shape, splits):
