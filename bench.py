@@ -46,8 +46,8 @@ def parse():
     p.add_argument("--kv-len", type=int, default=2048)
     p.add_argument("--backend", default="penny", choices=["penny", "penny_unfused", "nccl"])
     p.add_argument("--proto", default="auto", choices=["auto", "ll", "ll_twoshot", "flag", "nvls", "nvls_oneshot"])
-    p.add_argument("--linears", default="penny", choices=["penny", "cublas"],
-                   help="penny: this library's tcgen05 decode GEMM (default); cublas: torch.matmul, for comparison")
+    p.add_argument("--linears", default="auto", choices=["auto", "penny", "cublas"],
+                   help="auto: this library's tcgen05 decode GEMM up to 128 rows, the library GEMM above; penny / cublas force one")
     p.add_argument("--layers", type=int, default=32, help="debug only: anything but 32 is not the named config")
     p.add_argument("--no-graph", action="store_true")
     return p.parse_args()
@@ -252,7 +252,7 @@ def run_penny(args):
                        "global_batch": args.batch, "seq_len": args.kv_len, "parallelism": f"tp{world}",
                        "cuda_graph": not args.no_graph,
                        "l2": "inputs larger than L2 (weights + KV streamed every step)"},
-            "impl_detail": {"backend": args.backend, "proto": model.proto, "linears": args.linears,
+            "impl_detail": {"backend": args.backend, "proto": model.proto, "linears": model.linears,
                             "programmatic_dependent_launch": bool(ops_pdl_enabled()),
                             "streamed_gb_per_gpu_per_step": round(
                                 (model.weight_bytes() - model.embed.numel() * 2

@@ -144,8 +144,16 @@ struct NvlsTwoShotStaged {
     // position j of EVERY rank's chunk belongs to the same (block, thread) on every rank
     for (int s = 0; s < c.world; ++s) {
       const Span sp = split_span(V, c.world, s);
-      for (size_t j = first; j < sp.end - sp.begin; j += stride)
-        st16(c.heap[rank] + in_base + (sp.begin + j) * 16, load_user_vec<T>(in, sp.begin + j, a.n));
+      const size_t n_s = sp.end - sp.begin;
+      for (size_t j0 = first; j0 < n_s; j0 += kBatch * stride) {
+        V16 r[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u)
+          if (j0 + u * stride < n_s) r[u] = load_user_vec<T>(in, sp.begin + j0 + u * stride, a.n);
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u)
+          if (j0 + u * stride < n_s) st16(c.heap[rank] + in_base + (sp.begin + j0 + u * stride) * 16, r[u]);
+      }
     }
     PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 1), s_abort);
     if (s_abort) return;
@@ -164,8 +172,16 @@ struct NvlsTwoShotStaged {
     if (s_abort) return;
     for (int s = 0; s < c.world; ++s) {
       const Span sp = split_span(V, c.world, s);
-      for (size_t j = first; j < sp.end - sp.begin; j += stride)
-        store_user_vec<T>(out, sp.begin + j, a.n, ld16(c.heap[rank] + out_base + (sp.begin + j) * 16));
+      const size_t n_s = sp.end - sp.begin;
+      for (size_t j0 = first; j0 < n_s; j0 += kBatch * stride) {
+        V16 r[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u)
+          if (j0 + u * stride < n_s) r[u] = ld16(c.heap[rank] + out_base + (sp.begin + j0 + u * stride) * 16);
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u)
+          if (j0 + u * stride < n_s) store_user_vec<T>(out, sp.begin + j0 + u * stride, a.n, r[u]);
+      }
     }
   }
   static __device__ void run(const CommCtx& c, int rank, const CollArgs& a, const Blk& b) {

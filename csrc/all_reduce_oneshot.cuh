@@ -105,6 +105,13 @@ PK_DEV bool ll_wait_line(const char* p, uint32_t e, V16& line, const CommCtx& c,
     }
   }
 }
+// `line` already holds one volatile load of *p: done if its stamps match, else keep polling.
+// Callers issue the first loads of all the lines they need back to back and only then look at
+// them, so lines that have already landed cost one memory latency in total, not one each.
+PK_DEV bool ll_finish_line(const char* p, uint32_t e, V16& line, const CommCtx& c, int peer, int bid) {
+  if (line.w[1] == e && line.w[3] == e) return true;
+  return ll_wait_line(p, e, line, c, peer, bid);
+}
 // The flag carried by every LL line of call `seq`: never 0 (fresh memory).
 PK_HD uint32_t ll_flag(u64 seq) { return (uint32_t)(seq + 1) | 0x80000000u; }
 
@@ -142,17 +149,24 @@ struct OneShotLL {
 #pragma unroll
         for (size_t i = 0; i < E; ++i) acc[i] = 0.f;
         bool ok = true;
+        const char* src = c.heap[rank] + base;
+        V16 l0[NG], l1[NG];
+#pragma unroll
+        for (int s = 0; s < NG; ++s) {
+          if (s != rank) {
+            l0[s] = ld16_volatile(src + ll_line_off(vpad, s, v, 0));
+            l1[s] = ld16_volatile(src + ll_line_off(vpad, s, v, 1));
+          }
+        }
 #pragma unroll
         for (int s = 0; s < NG; ++s) {
           V16 x;
           if (s == rank) {
             x = load_user_vec<T>(in, v, a.n);
           } else {
-            const char* src = c.heap[rank] + base;
-            V16 l0, l1;
-            ok = ok && ll_wait_line(src + ll_line_off(vpad, s, v, 0), e, l0, c, s, b.bid);
-            ok = ok && ll_wait_line(src + ll_line_off(vpad, s, v, 1), e, l1, c, s, b.bid);
-            x.w[0] = l0.w[0]; x.w[1] = l0.w[2]; x.w[2] = l1.w[0]; x.w[3] = l1.w[2];
+            ok = ok && ll_finish_line(src + ll_line_off(vpad, s, v, 0), e, l0[s], c, s, b.bid);
+            ok = ok && ll_finish_line(src + ll_line_off(vpad, s, v, 1), e, l1[s], c, s, b.bid);
+            x.w[0] = l0[s].w[0]; x.w[1] = l0[s].w[2]; x.w[2] = l1[s].w[0]; x.w[3] = l1[s].w[2];
           }
           unpack_add<T>(x, acc);
         }

@@ -315,7 +315,7 @@ void Communicator::run_all_reduce_once(int algo, int dtype, const void* const* i
         // tensors outside the heap, small enough that two extra copy launches would cost more than
         // copying inside the kernel: one launch, staged through this call's scratch half
         set_scratch(ensure(scratch_, nvls_staged_scratch(n, es), "NVLS staged"));
-        rc = launch_all_reduce_nvls(dtype, NVLS_STAGED, ctx_, a, cfg_for(ceil_div(V, world_), t, stream, 64, 1, 2));
+        rc = launch_all_reduce_nvls(dtype, NVLS_STAGED, ctx_, a, cfg_for(V, t, stream, 64, 1, 2));  // sized for the copies
         break;
       }
       // large: the copy engines' rate matters more than two launches

@@ -90,13 +90,45 @@ void bind_decode(py::module_& m) {
     const at::cuda::OptionalCUDAGuard guard(gate_up.device());
     ck(launch_silu_mul(gate_up.data_ptr(), out.data_ptr(), (int)rows, (int)F, cur()), "silu_mul");
   });
-  m.def("argmax_rows", [](at::Tensor logits, at::Tensor out_val, at::Tensor out_idx, int64_t index_base) {
+  m.def("argmax_workspace_bytes", [](int64_t rows) { return (int64_t)argmax_workspace_bytes((int)rows); });
+  m.def("argmax_rows", [](at::Tensor logits, at::Tensor out_val, at::Tensor out_idx, int64_t index_base,
+                          c10::optional<at::Tensor> workspace, c10::optional<at::Tensor> pair) {
     need(bf16_cuda(logits) && logits.dim() == 2, "argmax_rows expects [rows, cols] bf16");
-    need(out_val.is_cuda() && out_val.scalar_type() == at::kFloat && out_val.numel() == logits.size(0), "out_val [rows] fp32");
-    need(out_idx.is_cuda() && out_idx.scalar_type() == at::kLong && out_idx.numel() == logits.size(0), "out_idx [rows] int64");
+    const int64_t rows = logits.size(0);
+    need(out_val.is_cuda() && out_val.scalar_type() == at::kFloat && out_val.numel() == rows, "out_val [rows] fp32");
+    need(out_idx.is_cuda() && out_idx.scalar_type() == at::kLong && out_idx.numel() == rows, "out_idx [rows] int64");
+    void* ws = nullptr;
+    if (workspace.has_value()) {
+      need(workspace->is_cuda() && workspace->is_contiguous() &&
+               (int64_t)workspace->nbytes() >= (int64_t)argmax_workspace_bytes((int)rows),
+           "workspace too small (argmax_workspace_bytes) or not contiguous; it must be zeroed once");
+      ws = workspace->data_ptr();
+    }
+    float* pp = nullptr;
+    if (pair.has_value()) {
+      need(pair->is_cuda() && pair->scalar_type() == at::kFloat && pair->is_contiguous() && pair->numel() == 2 * rows,
+           "pair [2 * rows] fp32");
+      pp = pair->data_ptr<float>();
+    }
     const at::cuda::OptionalCUDAGuard guard(logits.device());
-    ck(launch_argmax(logits.data_ptr(), (int)logits.size(0), (int)logits.size(1), out_val.data_ptr<float>(),
-                     (long long*)out_idx.data_ptr<int64_t>(), (long long)index_base, cur()),
+    ck(launch_argmax(logits.data_ptr(), (int)rows, (int)logits.size(1), out_val.data_ptr<float>(),
+                     (long long*)out_idx.data_ptr<int64_t>(), pp, (long long)index_base, ws, cur()),
        "argmax_rows");
+  }, py::arg("logits"), py::arg("out_val"), py::arg("out_idx"), py::arg("index_base"),
+     py::arg("workspace") = py::none(), py::arg("pair") = py::none());
+  m.def("sample_finish", [](at::Tensor pairs, int64_t world, at::Tensor next_tokens, at::Tensor tokens,
+                            at::Tensor positions) {
+    const int64_t B = next_tokens.numel();
+    need(pairs.is_cuda() && pairs.scalar_type() == at::kFloat && pairs.is_contiguous() && pairs.numel() == world * 2 * B,
+         "pairs [world, 2, B] fp32");
+    need(next_tokens.scalar_type() == at::kLong && tokens.scalar_type() == at::kLong && tokens.numel() == B &&
+             positions.scalar_type() == at::kInt && positions.numel() == B && next_tokens.is_cuda() &&
+             tokens.is_cuda() && positions.is_cuda(),
+         "next_tokens / tokens [B] int64, positions [B] int32");
+    const at::cuda::OptionalCUDAGuard guard(pairs.device());
+    ck(launch_sample_finish(pairs.data_ptr<float>(), (int)world, (int)B, (long long*)next_tokens.data_ptr<int64_t>(),
+                            (long long*)tokens.data_ptr<int64_t>(), positions.data_ptr<int>(), cur()),
+       "sample_finish");
   });
+
 }

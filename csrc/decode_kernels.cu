@@ -18,6 +18,7 @@
 
 #include <stdio.h>
 
+#include <algorithm>
 #include <mutex>
 
 #include "decode_attention_noalloc.h"
@@ -314,56 +315,123 @@ __global__ void k_silu_mul(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* 
   }
 }
 
-// Per-row arg-max over a vocabulary shard.  grid = rows, block = 256.
-// out_val[row], out_idx[row] (index offset by `index_base`).
-__global__ void __launch_bounds__(256) k_argmax(const __nv_bfloat16* __restrict__ logits, int cols,
-                                                float* __restrict__ out_val,
-                                                long long* __restrict__ out_idx,
-                                                long long index_base) {
+// Per-row arg-max over a vocabulary shard.  grid = (chunks, rows), block = 256: a row is cut into
+// `chunks` column ranges so that rows x chunks blocks fill the GPU and every thread streams 16-byte
+// vectors; the block that finishes a row last (a counter per row in `workspace`, left at zero again)
+// merges the chunk results.  out_val[row], out_idx[row] (index offset by `index_base`); `pair`,
+// when given, also receives [rows] values followed by [rows] indices as fp32 (the layout the
+// tensor-parallel sampler all-gathers).  Ties: the lowest index.
+constexpr int kArgmaxMaxChunks = 32;
+
+__device__ __forceinline__ void argmax_take(float v, int i, float& best, int& bi) {
+  if (v > best || (v == best && i < bi)) {
+    best = v;
+    bi = i;
+  }
+}
+
+__global__ void __launch_bounds__(256) k_argmax(const __nv_bfloat16* __restrict__ logits, int cols, int per,
+                                                float* __restrict__ out_val, long long* __restrict__ out_idx,
+                                                float* __restrict__ pair, long long index_base,
+                                                unsigned int* __restrict__ workspace) {
   __shared__ float sval[8];
   __shared__ int sidx[8];
-  const __nv_bfloat16* row = logits + (size_t)blockIdx.x * cols;
+  __shared__ bool s_last;
+  const int rows = (int)gridDim.y, chunks = (int)gridDim.x, r = (int)blockIdx.y, ch = (int)blockIdx.x;
+  const __nv_bfloat16* row = logits + (size_t)r * cols;
+  const int c0 = ch * per, c1 = min(cols, c0 + per);
   float best = -INFINITY;
-  int bi = 0;
-  for (int i = threadIdx.x; i < cols; i += blockDim.x) {
-    const float v = bf2f(row[i]);
-    if (v > best) {
-      best = v;
-      bi = i;
-    }
-  }
+  int bi = 0x7fffffff;
+  if ((reinterpret_cast<uintptr_t>(row + c0) & 15u) == 0) {
+    const int nvec = (c1 - c0) / 8;
+    const uint4* vp = reinterpret_cast<const uint4*>(row + c0);
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      const uint4 q = vp[i];
+      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&q);
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > best || (ov == best && oi < bi)) {
-      best = ov;
-      bi = oi;
+      for (int k = 0; k < 8; ++k) argmax_take(bf2f(e[k]), c0 + i * 8 + k, best, bi);
     }
+    for (int i = c0 + nvec * 8 + threadIdx.x; i < c1; i += blockDim.x) argmax_take(bf2f(row[i]), i, best, bi);
+  } else {
+    for (int i = c0 + threadIdx.x; i < c1; i += blockDim.x) argmax_take(bf2f(row[i]), i, best, bi);
   }
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (lane == 0) {
-    sval[warp] = best;
-    sidx[warp] = bi;
-  }
-  __syncthreads();
-  if (warp == 0) {
+  auto block_best = [&]() {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      argmax_take(ov, oi, best, bi);
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) {
+      sval[warp] = best;
+      sidx[warp] = bi;
+    }
+    __syncthreads();
     best = lane < 8 ? sval[lane] : -INFINITY;
     bi = lane < 8 ? sidx[lane] : 0x7fffffff;
 #pragma unroll
     for (int o = 4; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, best, o);
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) {
-        best = ov;
-        bi = oi;
-      }
+      argmax_take(ov, oi, best, bi);
     }
-    if (lane == 0) {
-      out_val[blockIdx.x] = best;
-      out_idx[blockIdx.x] = index_base + bi;
+  };
+  block_best();  // threads of warp 0 hold the chunk's result
+  unsigned int* counter = workspace + r;
+  float* part_val = reinterpret_cast<float*>(workspace + rows) + (size_t)r * kArgmaxMaxChunks;
+  int* part_idx = reinterpret_cast<int*>(workspace + rows + (size_t)rows * kArgmaxMaxChunks) + (size_t)r * kArgmaxMaxChunks;
+  if (chunks > 1) {
+    if (threadIdx.x == 0) {
+      part_val[ch] = best;
+      part_idx[ch] = bi;
+      __threadfence();
+      s_last = atomicAdd(counter, 1u) == (unsigned)chunks - 1u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    best = -INFINITY;
+    bi = 0x7fffffff;
+    if (threadIdx.x < chunks) {
+      best = __ldcg(part_val + threadIdx.x);
+      bi = __ldcg(part_idx + threadIdx.x);
+    }
+    block_best();
+    if (threadIdx.x == 0) *counter = 0;  // ready for the next launch
+  }
+  if (threadIdx.x == 0) {
+    if (bi == 0x7fffffff) bi = 0;  // nothing compared greater than -inf (an all-NaN row)
+    out_val[r] = best;
+    out_idx[r] = index_base + bi;
+    if (pair != nullptr) {
+      pair[r] = best;
+      pair[rows + r] = (float)(index_base + bi);  // vocabularies stay below 2^24: exact
     }
   }
+}
+
+// End of a greedy decode step in one launch: pick, per sequence, the rank whose shard holds the
+// largest logit (pairs: [world][2][B] fp32 = values, indices; lowest rank on ties), hand the token
+// to the next step and advance the positions.
+__global__ void k_sample_finish(const float* __restrict__ pairs, int world, int B, long long* __restrict__ next_tokens,
+                                long long* __restrict__ tokens, int* __restrict__ positions) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  float best = pairs[b];
+  float idx = pairs[B + b];
+  for (int w = 1; w < world; ++w) {
+    const float v = pairs[(size_t)w * 2 * B + b];
+    if (v > best) {
+      best = v;
+      idx = pairs[(size_t)w * 2 * B + B + b];
+    }
+  }
+  const long long t = (long long)idx;
+  next_tokens[b] = t;
+  tokens[b] = t;
+  positions[b] += 1;
 }
 
 }  // namespace
@@ -432,10 +500,30 @@ cudaError_t launch_silu_mul(const void* gate_up, void* out, int rows, int F, cud
   return cudaGetLastError();
 }
 
-cudaError_t launch_argmax(const void* logits, int rows, int cols, float* out_val, long long* out_idx,
-                          long long index_base, cudaStream_t stream) {
-  k_argmax<<<rows, 256, 0, stream>>>((const __nv_bfloat16*)logits, cols, out_val, out_idx,
-                                     index_base);
+size_t argmax_workspace_bytes(int rows) {
+  return (size_t)rows * 4 + (size_t)rows * kArgmaxMaxChunks * 8;
+}
+
+cudaError_t launch_argmax(const void* logits, int rows, int cols, float* out_val, long long* out_idx, float* pair,
+                          long long index_base, void* workspace, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0 || rows > 65535) return cudaErrorInvalidValue;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  // enough blocks for two per SM, no chunk below 2048 columns; one chunk when there is no workspace
+  int chunks = workspace == nullptr ? 1 : std::min({kArgmaxMaxChunks, (2 * sms + rows - 1) / rows, std::max(1, cols / 2048)});
+  chunks = std::max(chunks, 1);
+  int per = ((cols + chunks - 1) / chunks + 7) / 8 * 8;
+  chunks = (cols + per - 1) / per;
+  k_argmax<<<dim3((unsigned)chunks, (unsigned)rows), 256, 0, stream>>>((const __nv_bfloat16*)logits, cols, per, out_val,
+                                                                     out_idx, pair, index_base,
+                                                                     (unsigned int*)workspace);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_sample_finish(const float* pairs, int world, int B, long long* next_tokens, long long* tokens,
+                                 int* positions, cudaStream_t stream) {
+  if (world < 1 || B <= 0) return cudaErrorInvalidValue;
+  k_sample_finish<<<(B + 127) / 128, 128, 0, stream>>>(pairs, world, B, next_tokens, tokens, positions);
   return cudaGetLastError();
 }
 

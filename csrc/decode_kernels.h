@@ -39,8 +39,15 @@ cudaError_t launch_decode_attention_fused(const void* qkv, void* kcache, void* v
 // gate_up: [rows, 2F] (gate | up) -> out [rows, F] = silu(gate) * up
 cudaError_t launch_silu_mul(const void* gate_up, void* out, int rows, int F, cudaStream_t stream);
 
-// logits: [rows, cols] bf16 -> per-row max value and index (+ index_base)
-cudaError_t launch_argmax(const void* logits, int rows, int cols, float* out_val, long long* out_idx,
-                          long long index_base, cudaStream_t stream);
+// logits: [rows, cols] bf16 -> per-row max value and index (+ index_base).  workspace: zeroed once,
+// argmax_workspace_bytes(rows) bytes (nullptr: one block per row); pair: optional [2 * rows] fp32
+// (values, then indices).
+size_t argmax_workspace_bytes(int rows);
+cudaError_t launch_argmax(const void* logits, int rows, int cols, float* out_val, long long* out_idx, float* pair,
+                          long long index_base, void* workspace, cudaStream_t stream);
+// pairs: [world][2][B] fp32 (values, indices) -> next_tokens[B] = tokens[B] = index of the largest
+// value over the ranks; positions[B] += 1.
+cudaError_t launch_sample_finish(const float* pairs, int world, int B, long long* next_tokens, long long* tokens,
+                                 int* positions, cudaStream_t stream);
 
 }  // namespace penny

@@ -165,6 +165,18 @@ struct FusedOneShotNorm {
           nv = k + 1;
 #pragma unroll
           for (int i = 0; i < E; ++i) z[k][i] = 0.f;
+          // first loads of every peer's lines back to back; then wait for the late ones
+          V16 l0[NG], l1[NG];
+          if (LL) {
+#pragma unroll
+            for (int s = 0; s < NG; ++s) {
+              if (s != rank) {
+                const char* src = c.heap[rank] + base + (((size_t)s * a.rows + row) * HV + v) * LINE;
+                l0[s] = ld16_volatile(src);
+                l1[s] = ld16_volatile(src + 16);
+              }
+            }
+          }
 #pragma unroll
           for (int s = 0; s < NG; ++s) {
             V16 x;
@@ -173,10 +185,9 @@ struct FusedOneShotNorm {
             } else {
               const char* src = c.heap[rank] + base + (((size_t)s * a.rows + row) * HV + v) * LINE;
               if (LL) {
-                V16 l0, l1;
-                ok = ok && ll_wait_line(src, e, l0, c, s, b.bid);
-                ok = ok && ll_wait_line(src + 16, e, l1, c, s, b.bid);
-                x.w[0] = l0.w[0]; x.w[1] = l0.w[2]; x.w[2] = l1.w[0]; x.w[3] = l1.w[2];
+                ok = ok && ll_finish_line(src, e, l0[s], c, s, b.bid);
+                ok = ok && ll_finish_line(src + 16, e, l1[s], c, s, b.bid);
+                x.w[0] = l0[s].w[0]; x.w[1] = l0[s].w[2]; x.w[2] = l1[s].w[0]; x.w[3] = l1[s].w[2];
               } else {
                 x = ld16(src);
               }
@@ -289,8 +300,8 @@ struct FusedTwoShotLLNorm {
         T* out = reinterpret_cast<T*>(a.out) + row * (size_t)a.hidden;
         for (int v = threadIdx.x; v < HV && ok; v += blockDim.x) {
           const char* src = c.heap[rank] + p2 + ((size_t)row * HV + v) * 32;
-          V16 l0, l1, x;
-          ok = ll_wait_line(src, e, l0, c, owner, b.bid) && ll_wait_line(src + 16, e, l1, c, owner, b.bid);
+          V16 l0 = ld16_volatile(src), l1 = ld16_volatile(src + 16), x;
+          ok = ll_finish_line(src, e, l0, c, owner, b.bid) && ll_finish_line(src + 16, e, l1, c, owner, b.bid);
           x.w[0] = l0.w[0]; x.w[1] = l0.w[2]; x.w[2] = l1.w[0]; x.w[3] = l1.w[2];
           if (ok) st16(out + (size_t)v * E, x);
         }
@@ -307,6 +318,16 @@ struct FusedTwoShotLLNorm {
           nv = k + 1;
 #pragma unroll
           for (int i = 0; i < E; ++i) z[k][i] = 0.f;
+          // first loads of every peer's lines back to back; then wait for the late ones
+          V16 l0[NG], l1[NG];
+#pragma unroll
+          for (int s = 0; s < NG; ++s) {
+            if (s != rank) {
+              const char* src = c.heap[rank] + base + (((size_t)s * per + lrow) * HV + v) * 32;
+              l0[s] = ld16_volatile(src);
+              l1[s] = ld16_volatile(src + 16);
+            }
+          }
 #pragma unroll
           for (int s = 0; s < NG; ++s) {
             V16 x;
@@ -314,10 +335,9 @@ struct FusedTwoShotLLNorm {
               x = ld16(in + row * a.hidden + (size_t)v * E);
             } else {
               const char* src = c.heap[rank] + base + (((size_t)s * per + lrow) * HV + v) * 32;
-              V16 l0, l1;
-              ok = ok && ll_wait_line(src, e, l0, c, s, b.bid);
-              ok = ok && ll_wait_line(src + 16, e, l1, c, s, b.bid);
-              x.w[0] = l0.w[0]; x.w[1] = l0.w[2]; x.w[2] = l1.w[0]; x.w[3] = l1.w[2];
+              ok = ok && ll_finish_line(src, e, l0[s], c, s, b.bid);
+              ok = ok && ll_finish_line(src + 16, e, l1[s], c, s, b.bid);
+              x.w[0] = l0[s].w[0]; x.w[1] = l0[s].w[2]; x.w[2] = l1[s].w[0]; x.w[3] = l1[s].w[2];
             }
             unpack_add<T>(x, z[k]);
           }

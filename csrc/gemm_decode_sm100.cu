@@ -92,6 +92,7 @@ struct DecodeArgs {
   int k_stagger;    // 1: tiles start their K range at different offsets
   int stamps;       // 1: record timestamps
   int epi;          // DECODE_EPI_*
+  int slabs;        // batch slabs of BT rows (1 unless B > 128)
   DecodePush push;  // world == 0: plain store
 };
 
@@ -164,7 +165,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   pdl_launch_dependents();
-  const int cta_lin = (int)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x);
+  const int cta_lin = (int)(blockIdx.y * gridDim.x + blockIdx.x);
   auto stamp = [&](int point) {
     if (a.stamps && cta_lin < kStampCtas) g_dec_stamps[cta_lin * kStampPoints + point] = gtime_ns();
   };
@@ -172,8 +173,10 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t crank = S > 1 ? cluster_ctarank() : 0u;
-  const int tile = (int)blockIdx.y;
-  const int row0 = (int)blockIdx.z * BT;  // batch slab of this CTA (batches above BT rows: one slab per grid z)
+  // batches above BT rows: grid y = tile * slabs + slab, so the slabs of a weight tile are dispatched
+  // next to each other and read the tile from DRAM once
+  const int tile = (int)blockIdx.y / a.slabs;
+  const int row0 = ((int)blockIdx.y % a.slabs) * BT;
   const int kb0 = decode_kb_begin(a.num_kb, S, (int)crank), kb1 = decode_kb_begin(a.num_kb, S, (int)crank + 1);
   const int nkb = kb1 - kb0;
   const int sl = decode_slice(BT, S);
@@ -504,7 +507,9 @@ cudaError_t launch_decode_bt(const void* x, const void* w, void* out, int B, int
   a.K = K;
   a.num_kb = (K + kBlockK - 1) / kBlockK;
   const int tiles = (N + kBlockM - 1) / kBlockM;
-  const int slabs = (B + BT - 1) / BT;  // > 1 only with BT = 128: the slabs of a tile run side by side and share W in L2
+  const int slabs = (B + BT - 1) / BT;  // > 1 only with BT = 128
+  if ((long long)tiles * slabs > 65535) return cudaErrorInvalidValue;
+  a.slabs = slabs;
   if (splits <= 0) splits = decode_choose_splits(tiles * slabs, a.num_kb, decode_capacity<BT>(sms));
   splits = std::max(1, std::min(splits, std::min(kDecodeMaxSplits, a.num_kb)));
   a.splits = splits;
@@ -535,7 +540,7 @@ cudaError_t launch_decode_bt(const void* x, const void* w, void* out, int B, int
   a.stamps = env_stamps;
   rc = kernel_setup(reinterpret_cast<const void*>(gemm_decode_kernel<BT>), 227 << 10).rc;
   if (rc != cudaSuccess) return rc;
-  return launch_kernel_ex(gemm_decode_kernel<BT>, dim3((unsigned)splits, (unsigned)tiles, (unsigned)slabs), dim3(kDecThreads), smem,
+  return launch_kernel_ex(gemm_decode_kernel<BT>, dim3((unsigned)splits, (unsigned)(tiles * slabs), 1), dim3(kDecThreads), smem,
                           stream, pdl, splits, mw, mx, a, error_word);
 }
 

@@ -24,7 +24,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--batches", type=int, nargs="*", default=[64])
     ap.add_argument("--protos", nargs="*", default=["auto"])
-    ap.add_argument("--linears", nargs="*", default=["penny"])
+    ap.add_argument("--linears", nargs="*", default=["auto"])
     ap.add_argument("--backends", nargs="*", default=["penny"])
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--kv-len", type=int, default=2048)
@@ -73,7 +73,7 @@ def main():
                             comm.check()
                         if rank == 0:
                             print(json.dumps({"world": world, "batch": batch, "backend": backend, "proto": model.proto,
-                                              "asked_proto": proto, "linears": linears, "pdl": pdl,
+                                              "asked_proto": proto, "linears": model.linears, "pdl": pdl,
                                               "ms_per_step": round(ms, 4), "tokens_per_s": round(batch / ms * 1e3, 1)}),
                                   flush=True)
                         del model

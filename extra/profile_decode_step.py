@@ -41,7 +41,7 @@ def main():
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--kv-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=32)
-    ap.add_argument("--linears", default="penny", choices=["penny", "cublas"])
+    ap.add_argument("--linears", default="auto", choices=["auto", "penny", "cublas"])
     ap.add_argument("--backend", default="penny", choices=["penny", "penny_unfused", "nccl"])
     ap.add_argument("--proto", default="auto")
     args = ap.parse_args()
@@ -77,7 +77,7 @@ def main():
         per_step = len(ev) // steps
         last = ev[-per_step:]
         t0, t1 = last[0].time_range.start, max(e.time_range.end for e in last)
-        print(f"world {world}, batch {args.batch}, kv {args.kv_len}, linears {args.linears}, proto {model.proto}: "
+        print(f"world {world}, batch {args.batch}, kv {args.kv_len}, linears {model.linears}, proto {model.proto}: "
               f"{per_step} kernels per step, step {t1 - t0:.1f} us (first kernel start to last kernel end)")
         agg = defaultdict(lambda: [0, 0.0])
         for e in last:

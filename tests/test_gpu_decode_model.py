@@ -132,6 +132,32 @@ def test_silu_mul_and_argmax():
     assert torch.equal(val, wv)
     # ties: any index holding the max is acceptable, the kernel returns the lowest
     assert torch.equal(logits.float().gather(1, (idx - 1000)[:, None]).squeeze(1), wv)
+    # rows cut into chunks (workspace given), ragged and unaligned widths, the (value, index) pair output,
+    # twice in a row on the same workspace (the row counters must be back at zero)
+    for rows, cols in ((9, 16032), (64, 128256), (3, 1001), (1, 7), (200, 4099)):
+        logits = torch.randn(rows, cols, device="cuda").bfloat16()
+        logits[0, cols // 2] = 9.0
+        logits[0, cols - 1] = 9.0  # a tie: the lower index wins
+        ws = torch.zeros(ops.argmax_workspace_bytes(rows), dtype=torch.uint8, device="cuda")
+        val = torch.empty(rows, device="cuda")
+        idx = torch.empty(rows, dtype=torch.int64, device="cuda")
+        pair = torch.empty(2 * rows, device="cuda")
+        for _ in range(2):
+            ops.argmax_rows(logits, val, idx, 5, ws, pair)
+            wv, _ = logits.float().max(-1)
+            assert torch.equal(val, wv) and int(idx[0]) == 5 + cols // 2
+            assert torch.equal(logits.float().gather(1, (idx - 5)[:, None]).squeeze(1), wv)
+            assert torch.equal(pair[:rows], wv) and torch.equal(pair[rows:].long(), idx)
+    # the end of a greedy step: best rank per sequence, token fed back, positions advanced
+    world, B = 4, 5
+    pairs = torch.zeros(world, 2, B, device="cuda")
+    pairs[:, 0] = torch.tensor([[1., 5, 2, 0, 3], [4, 5, 1, 0, 2], [0, 1, 9, 0, 3], [2, 2, 2, 0, 8]], device="cuda")
+    pairs[:, 1] = torch.arange(world * B, device="cuda").view(world, B).float() + 100
+    nxt = torch.zeros(B, dtype=torch.int64, device="cuda")
+    tok = torch.zeros(B, dtype=torch.int64, device="cuda")
+    pos = torch.full((B,), 7, dtype=torch.int32, device="cuda")
+    ops.sample_finish(pairs, world, nxt, tok, pos)
+    assert nxt.tolist() == [105, 101, 112, 103, 119] and torch.equal(tok, nxt) and pos.tolist() == [8] * B
 
 
 @pytest.mark.parametrize("use_graph", [False, True])
