@@ -26,6 +26,9 @@ constexpr size_t kScratchCap = (size_t)512 << 20;  // a single call never asks f
 // Switch all-reduce of tensors outside the heap: up to this size the staging copies run inside the
 // kernel (one launch instead of three); above it the copy engines' rate wins.
 constexpr size_t kNvlsStageInKernelBytes = (size_t)1 << 20;
+// ... and from this size the staging copies are pipelined against the reduction, piece by piece
+constexpr size_t kNvlsPipelineBytes = (size_t)256 << 20;  // below, the extra launches and events cost more than the overlap saves (measured)
+constexpr int kNvlsPipePieces = 4;
 }  // namespace
 
 Communicator::Communicator(const std::string& uid, int rank, int world, const CommOptions& opt)
@@ -60,9 +63,22 @@ void Communicator::init_ctx(const CommOptions& opt) {
     throw std::runtime_error("penny: heap too small");
 }
 
+void Communicator::ensure_pipe() {
+  if (pipe_in_ != nullptr) return;
+  ckrt(cudaStreamCreateWithFlags(&pipe_in_, cudaStreamNonBlocking), "pipeline stream");
+  ckrt(cudaStreamCreateWithFlags(&pipe_out_, cudaStreamNonBlocking), "pipeline stream");
+  pipe_ev_.resize(2 + 2 * kNvlsPipePieces);
+  for (cudaEvent_t& e : pipe_ev_) ckrt(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "pipeline event");
+}
+
 void Communicator::destroy() {
   if (destroyed_) return;
   destroyed_ = true;
+  for (cudaEvent_t e : pipe_ev_) cudaEventDestroy(e);
+  pipe_ev_.clear();
+  if (pipe_in_ != nullptr) cudaStreamDestroy(pipe_in_);
+  if (pipe_out_ != nullptr) cudaStreamDestroy(pipe_out_);
+  pipe_in_ = pipe_out_ = nullptr;
   if (heap_) heap_->destroy();
 }
 
@@ -319,22 +335,59 @@ void Communicator::run_all_reduce_once(int algo, int dtype, const void* const* i
         break;
       }
       // large: the copy engines' rate matters more than two launches
+      const size_t in_off0 = in_heap ? a[0].in_heap_off : ensure(stage_in_, bytes, "NVLS input staging").off;
+      const size_t out_off0 = out_heap ? out_off : ensure(stage_out_, bytes, "NVLS output staging").off;
+      if (bytes < kNvlsPipelineBytes) {
+        if (!in_heap)
+          ckrt(cudaMemcpyAsync(local_ptr(in_off0), in[0], n * es, cudaMemcpyDeviceToDevice, stream), "stage in");
+        a[0].in_heap_off = in_off0;
+        a[0].out_heap_off = out_off0;
+        rc = launch_all_reduce_nvls(dtype, NVLS_TWOSHOT, ctx_, a, cfg_for(ceil_div(V, world_), t, stream, 64, 1));
+        if (rc == cudaSuccess && !out_heap)
+          ckrt(cudaMemcpyAsync(out[0], local_ptr(out_off0), n * es, cudaMemcpyDeviceToDevice, stream), "stage out");
+        break;
+      }
+      // Very large: cut into pieces; the copy into the heap of piece i + 1 and the copy out of piece
+      // i - 1 run on two side streams under the switch reduction of piece i.  The reductions stay on
+      // the caller's stream, in the same order on every rank.  Works under stream capture: the side
+      // streams fork from and join back into the caller's stream through events.
+      ensure_pipe();
+      const size_t piece = round_up(ceil_div(n, (size_t)kNvlsPipePieces), 4096);  // elements; 16-byte multiple
+      ckrt(cudaEventRecord(pipe_ev_[0], stream), "pipeline fork");
       if (!in_heap) {
-        ensure(stage_in_, bytes, "NVLS input staging");
-        ckrt(cudaMemcpyAsync(local_ptr(stage_in_.off), in[0], n * es, cudaMemcpyDeviceToDevice,
-                             stream), "stage in");
-        a[0].in_heap_off = stage_in_.off;
+        ckrt(cudaStreamWaitEvent(pipe_in_, pipe_ev_[0], 0), "pipeline fork");
+        int i = 0;
+        for (size_t o = 0; o < n; o += piece, ++i) {
+          const size_t len = std::min(piece, n - o);
+          ckrt(cudaMemcpyAsync((char*)local_ptr(in_off0) + o * es, (const char*)in[0] + o * es, len * es,
+                               cudaMemcpyDeviceToDevice, pipe_in_), "stage in");
+          ckrt(cudaEventRecord(pipe_ev_[1 + i], pipe_in_), "stage in");
+        }
+      }
+      {
+        int i = 0;
+        for (size_t o = 0; o < n && rc == cudaSuccess; o += piece, ++i) {
+          const size_t len = std::min(piece, n - o);
+          if (!in_heap) ckrt(cudaStreamWaitEvent(stream, pipe_ev_[1 + i], 0), "stage in");
+          a[0].n = len;
+          a[0].in = (const char*)in[0] + o * es;
+          a[0].out = (char*)out[0] + o * es;
+          a[0].in_heap_off = in_off0 + o * es;
+          a[0].out_heap_off = out_off0 + o * es;
+          rc = launch_all_reduce_nvls(dtype, NVLS_TWOSHOT, ctx_, a,
+                                      cfg_for(ceil_div(vecs_for(len, es), world_), t, stream, 64, 1));
+          if (rc == cudaSuccess && !out_heap) {
+            ckrt(cudaEventRecord(pipe_ev_[1 + kNvlsPipePieces + i], stream), "stage out");
+            ckrt(cudaStreamWaitEvent(pipe_out_, pipe_ev_[1 + kNvlsPipePieces + i], 0), "stage out");
+            ckrt(cudaMemcpyAsync((char*)out[0] + o * es, (char*)local_ptr(out_off0) + o * es, len * es,
+                                 cudaMemcpyDeviceToDevice, pipe_out_), "stage out");
+          }
+        }
       }
       if (!out_heap) {
-        ensure(stage_out_, bytes, "NVLS output staging");
-        a[0].out_heap_off = stage_out_.off;
-      } else {
-        a[0].out_heap_off = out_off;
+        ckrt(cudaEventRecord(pipe_ev_[1 + 2 * kNvlsPipePieces], pipe_out_), "pipeline join");
+        ckrt(cudaStreamWaitEvent(stream, pipe_ev_[1 + 2 * kNvlsPipePieces], 0), "pipeline join");
       }
-      rc = launch_all_reduce_nvls(dtype, NVLS_TWOSHOT, ctx_, a, cfg_for(ceil_div(V, world_), t, stream, 64, 1));
-      if (rc == cudaSuccess && !out_heap)
-        ckrt(cudaMemcpyAsync(out[0], local_ptr(stage_out_.off), n * es, cudaMemcpyDeviceToDevice,
-                             stream), "stage out");
       break;
     }
     default:

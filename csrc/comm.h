@@ -159,6 +159,11 @@ class Communicator {
   Region scratch_ll_;    // halved, LL lines only
   Region scratch_pair_;  // exchange slot
   Region stage_in_, stage_out_;  // NVLS staging for tensors outside the heap
+  // side streams + events that overlap the staging copies of a very large switch all-reduce with
+  // its reductions (created on first use)
+  void ensure_pipe();
+  cudaStream_t pipe_in_ = nullptr, pipe_out_ = nullptr;
+  std::vector<cudaEvent_t> pipe_ev_;
   // gathered A of all_gather_gemm: one dedicated region per (M, K), kept for the
   // communicator's lifetime and reused, so alternating shapes do not grow the heap
   std::map<std::pair<int, int>, Region> ag_regions_;

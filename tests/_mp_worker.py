@@ -29,7 +29,7 @@ def main():
     rank, world, _ = initialize_distributed(init_native=False)
     from penny_b200.parallel.comm import Communicator
     report = {"world": world, "failures": [], "checked": 0}
-    comm = Communicator.create(None, heap_bytes=1 << 30, multicast=use_nvls, timeout_ms=5000)
+    comm = Communicator.create(None, heap_bytes=2 << 30, multicast=use_nvls, timeout_ms=5000)
     report["describe"] = comm.describe()
     report["multicast"] = comm.has_multicast
 
@@ -44,6 +44,38 @@ def main():
     algos = ["oneshot", "oneshot_ll", "twoshot", "ring_simple", "ring_standard", "double_ring", "tree"]
     if comm.has_multicast:
         algos += ["nvls", "nvls_oneshot"]
+
+    if comm.has_multicast:
+        # a very large tensor in ordinary memory: the staging copies of the switch all-reduce run piece by
+        # piece on side streams under the reductions; eager, in place, and replayed from a CUDA graph
+        def run_pipelined_nvls():
+            n = (64 << 20) + 1000  # fp32: just above the size where the pipeline starts, ragged pieces
+            base = (torch.arange(n, device="cuda") % 251).float()
+            x = base + rank
+            want = base * world + sum(range(world))
+            out = comm.all_reduce(x, algo="nvls")
+            comm.check()
+            assert torch.equal(out, want), "eager"
+            y = x.clone()
+            comm.all_reduce(y, out=y, algo="nvls")
+            assert torch.equal(y, want), "in place"
+            o2 = torch.empty_like(x)
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                comm.all_reduce(x, out=o2, algo="nvls")
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                comm.all_reduce(x, out=o2, algo="nvls")
+            for _ in range(2):
+                o2.zero_()
+                gr.replay()
+                torch.cuda.synchronize()
+                assert torch.equal(o2, want), "graph replay"
+            comm.check()
+        check("all_reduce/nvls-pipelined-staging", run_pipelined_nvls)
 
     for dtype in (torch.float32, torch.bfloat16):
         for n in (1, 1023, 4096, 65536, 1 << 20):
