@@ -244,7 +244,13 @@ class Communicator:
     # -------------------------------------------------------------- collectives
     def all_reduce(self, inp: TensorOrList, out: Optional[TensorOrList] = None, algo="auto",
                    blocks: int = 0, threads: int = 0, nnodes: int = 1, routes: int = 0):
-        """algo: a name from ALGOS, the reference's ids 0-3, or "auto" (the measured table)."""
+        """algo: a name from ALGOS, the reference's ids 0-3, or "auto" (the measured table).
+
+        The switch algorithms take tensors anywhere in device memory: "nvls_oneshot" stages its input
+        inside the kernel (one flag exchange, every rank pulls the whole sum; in place is fine);
+        "nvls" reduces and multicasts in place for tensors from `empty()`, stages inside the kernel
+        up to 1 MiB, with two copies above that and, from 256 MiB, with the copies of piece i + 1 and
+        piece i - 1 running on side streams under the reduction of piece i."""
         ins = self._as_list(inp)
         outs = self._as_list(out) if out is not None else [torch.empty_like(x) for x in ins]
         if algo == "auto" and os.environ.get("PENNY_ALGO"):
