@@ -5,6 +5,7 @@
 #include <torch/extension.h>
 
 #include "decode_kernels.h"
+#include "moe_routing.h"
 
 namespace py = pybind11;
 using namespace penny;
@@ -116,6 +117,42 @@ void bind_decode(py::module_& m) {
        "argmax_rows");
   }, py::arg("logits"), py::arg("out_val"), py::arg("out_idx"), py::arg("index_base"),
      py::arg("workspace") = py::none(), py::arg("pair") = py::none());
+  // Expert-parallel MoE routing on the device (csrc/moe_routing.cu)
+  m.def("moe_route", [](at::Tensor logits, int64_t topk) {
+    need(bf16_cuda(logits) && logits.dim() == 2, "moe_route expects [tokens, experts] bf16");
+    const int64_t T = logits.size(0), E = logits.size(1);
+    const at::cuda::OptionalCUDAGuard guard(logits.device());
+    at::Tensor ids = at::empty({T, topk}, logits.options().dtype(at::kInt));
+    at::Tensor gates = at::empty({T, topk}, logits.options().dtype(at::kFloat));
+    ck(launch_moe_topk(logits.data_ptr(), (int)T, (int)E, (int)topk, ids.data_ptr<int>(), gates.data_ptr<float>(), cur()),
+       "moe_route");
+    return std::make_tuple(ids, gates);
+  });
+  m.def("moe_tables", [](at::Tensor ids, int64_t experts) {
+    need(ids.is_cuda() && ids.scalar_type() == at::kInt && ids.is_contiguous(), "moe_tables expects contiguous int32 ids");
+    const int64_t P = ids.numel();
+    const at::cuda::OptionalCUDAGuard guard(ids.device());
+    auto opt = ids.options();
+    at::Tensor order = at::empty({P}, opt), sorted = at::empty({P}, opt), send_off = at::empty({experts + 1}, opt),
+               counts = at::empty({experts}, opt);
+    ck(launch_moe_tables(ids.data_ptr<int>(), (int)P, (int)experts, order.data_ptr<int>(), sorted.data_ptr<int>(),
+                         send_off.data_ptr<int>(), counts.data_ptr<int>(), cur()),
+       "moe_tables");
+    return std::make_tuple(order, sorted, send_off, counts);
+  });
+  m.def("moe_placement", [](at::Tensor counts_all) {
+    need(counts_all.is_cuda() && counts_all.scalar_type() == at::kInt && counts_all.is_contiguous() &&
+             counts_all.dim() == 2,
+         "moe_placement expects [world, experts] int32");
+    const int64_t W = counts_all.size(0), E = counts_all.size(1);
+    const at::cuda::OptionalCUDAGuard guard(counts_all.device());
+    auto opt = counts_all.options();
+    at::Tensor dst_base = at::empty({W, E}, opt), rows = at::empty({W}, opt), ranges = at::empty({E, 2}, opt);
+    ck(launch_moe_placement(counts_all.data_ptr<int>(), (int)W, (int)E, dst_base.data_ptr<int>(), rows.data_ptr<int>(),
+                            ranges.data_ptr<int>(), cur()),
+       "moe_placement");
+    return std::make_tuple(dst_base, rows, ranges);
+  });
   m.def("sample_finish", [](at::Tensor pairs, int64_t world, at::Tensor next_tokens, at::Tensor tokens,
                             at::Tensor positions) {
     const int64_t B = next_tokens.numel();

@@ -47,13 +47,27 @@ class MoeConfig:
 
 def route(logits: torch.Tensor, topk: int):
     """Top-k routing: expert ids [T, k] (int32) and gate weights [T, k] (fp32,
-    softmax over the selected logits, as Mixtral does)."""
+    softmax over the selected logits, as Mixtral does).  One kernel for bf16 CUDA logits
+    (csrc/moe_routing.cu), torch ops otherwise."""
+    if logits.is_cuda and logits.dtype == torch.bfloat16 and logits.is_contiguous() and topk <= 8:
+        return ops.moe_route(logits, topk)
+    return route_torch(logits, topk)
+
+
+def route_torch(logits: torch.Tensor, topk: int):
     vals, ids = logits.float().topk(topk, dim=-1)
     return ids.to(torch.int32).contiguous(), torch.softmax(vals, dim=-1).contiguous()
 
 
 def build_routing(topk_ids: torch.Tensor, experts: int):
-    """Sender-side tables for one rank: pairs sorted by expert, per-expert counts."""
+    """Sender-side tables for one rank: pairs sorted by expert (stable), per-expert counts.
+    One kernel (a counting sort in one thread block) instead of sort + bincount + cumsum."""
+    if topk_ids.is_cuda and topk_ids.dtype == torch.int32 and experts <= 256:
+        return ops.moe_tables(topk_ids.reshape(-1).contiguous(), experts)
+    return build_routing_torch(topk_ids, experts)
+
+
+def build_routing_torch(topk_ids: torch.Tensor, experts: int):
     flat = topk_ids.reshape(-1).to(torch.int64)
     expert_sorted, order = torch.sort(flat, stable=True)
     counts = torch.bincount(flat, minlength=experts)
@@ -61,6 +75,19 @@ def build_routing(topk_ids: torch.Tensor, experts: int):
     send_off[1:] = counts.cumsum(0)
     return (order.to(torch.int32).contiguous(), expert_sorted.to(torch.int32).contiguous(),
             send_off.to(torch.int32).contiguous(), counts)
+
+
+def placement_device(counts_all: torch.Tensor):
+    """`placement` on the device: counts_all [W, E] int32 (CUDA) -> dst_base [W, E] int32 (stays on
+    the device for the dispatch kernel), and - the one host round trip of the layer, because the
+    expert GEMMs are launched with host-side shapes - rows_per_rank and per-rank expert ranges."""
+    W, E = counts_all.shape
+    dst_base, rows, ranges = ops.moe_placement(counts_all.contiguous())
+    host = torch.cat([rows, ranges.reshape(-1)]).cpu().tolist()
+    rows_per_rank, flat = host[:W], host[W:]
+    epr = E // W
+    expert_ranges = [[(flat[2 * (d * epr + le)], flat[2 * (d * epr + le) + 1]) for le in range(epr)] for d in range(W)]
+    return dst_base, rows_per_rank, expert_ranges
 
 
 def placement(counts_all: torch.Tensor, world: int):
@@ -164,13 +191,14 @@ class MoeEPLayer:
         if self.world > 1:
             gathered = comm.all_gather(self.counts_buf if comm.emulated else self.counts_buf[0])
             gathered = self._as_views(gathered)
-            counts_all = gathered[0].view(torch.int32).view(self.world, cfg.experts).cpu()
+            counts_dev = gathered[0].view(torch.int32).view(self.world, cfg.experts)
         else:
-            counts_all = tables[0][3].to(torch.int32).view(1, cfg.experts).cpu()
-        dst_base, rows_per_rank, expert_ranges = placement(counts_all, self.world)
+            counts_dev = tables[0][3].to(torch.int32).view(1, cfg.experts)
+        dst_base, rows_per_rank, expert_ranges = placement_device(counts_dev)
         if max(rows_per_rank) > self.cap_rows:
             raise RuntimeError(f"MoE capacity exceeded: {max(rows_per_rank)} rows > {self.cap_rows}")
-        dst_base_dev = [dst_base[r].to(self.dev).to(torch.int32).contiguous() for r in self.ranks]
+        dst_base_dev = [dst_base[r].contiguous() for r in self.ranks]
+        counts_all = counts_dev.cpu() if self.backend != "penny" else None  # the NCCL baseline wants split sizes
         L = (lambda t: t) if comm.emulated else (lambda t: t[0])
         if self.backend == "penny":
             comm.moe_dispatch(L(xs), L([t[0] for t in tables]), L([t[1] for t in tables]), L([t[2] for t in tables]),

@@ -61,14 +61,19 @@ class Tuner:
 
     # ---------------------------------------------------------------- building
     @classmethod
-    def from_sweep(cls, paths, dtype: Optional[str] = None, tolerance: float = 0.0) -> "Tuner":
+    def from_sweep(cls, paths, dtype: Optional[str] = None, tolerance: float = 0.0, both_dtypes=()) -> "Tuner":
         """Builds the table from one or several JSON-lines files.  Records need
         op, impl == "penny", algo, world, dtype, bytes and t_us (t_graph_us is preferred
         when present: it is what a call costs inside a serving engine's CUDA graph).
+        Several records of one point (re-measurements in later files): the fastest counts.
         tolerance: an algorithm within this fraction of the best keeps the previous
-        size's winner (fewer, longer rows)."""
+        size's winner (fewer, longer rows).
+        both_dtypes: files whose bf16 records also count for fp32 (a partial re-measurement in
+        one element size: every kernel moves 16-byte vectors, and in the full sweeps the two
+        differ by 1 % in the median at equal bytes)."""
         if isinstance(paths, str):
             paths = [paths]
+        paths = list(paths) + [p for p in both_dtypes if p not in paths]
         times: Dict[tuple, Dict[str, float]] = {}
         n_rec = 0
         for path in paths:
@@ -89,9 +94,13 @@ class Tuner:
                     if not t:
                         continue
                     mem = "sym" if r.get("symmetric") else "any"
-                    key = (r["op"], str(int(r["world"])), r.get("dtype", "bf16"), mem, int(r["bytes"]))
-                    slot = times.setdefault(key, {})
-                    slot[algo] = min(float(t), slot.get(algo, float("inf")))
+                    dts = [r.get("dtype", "bf16")]
+                    if path in both_dtypes and dts[0] == "bf16" and r["op"] != "fused_norm":
+                        dts.append("fp32")
+                    for dt in dts:
+                        key = (r["op"], str(int(r["world"])), dt, mem, int(r["bytes"]))
+                        slot = times.setdefault(key, {})
+                        slot[algo] = min(float(t), slot.get(algo, float("inf")))
                     n_rec += 1
         table: dict = {}
         prev_key, prev_algo = None, None
@@ -192,10 +201,12 @@ def _main(argv=None) -> int:
     ap.add_argument("--out", default=None, help=f"table file (default: PENNY_TUNER_CACHE or {DEFAULT_CACHE})")
     ap.add_argument("--builtin", action="store_true", help="write the package's built-in table instead")
     ap.add_argument("--dtype", default=None, help="only use records of this dtype (e.g. bf16)")
+    ap.add_argument("--both-dtypes", nargs="*", default=[],
+                    help="further sweep files whose bf16 records also count for fp32 (partial re-measurements)")
     ap.add_argument("--tolerance", type=float, default=0.03,
                     help="keep the previous size's winner while it is within this fraction of the best")
     args = ap.parse_args(argv)
-    t = Tuner.from_sweep(args.sweep, dtype=args.dtype, tolerance=args.tolerance)
+    t = Tuner.from_sweep(args.sweep, dtype=args.dtype, tolerance=args.tolerance, both_dtypes=args.both_dtypes)
     if not t.records:
         print("no usable records (impl=penny, a named algorithm) in", ", ".join(args.sweep))
         return 1

@@ -37,6 +37,7 @@ CUDA_SOURCES = [
     "csrc/gemm_fused_sm100.cu",
     "csrc/gemm_decode_sm100.cu",
     "csrc/moe_dispatch_combine.cu",
+    "csrc/moe_routing.cu",
 ]
 CPP_SOURCES = [
     "csrc/torch_interface.cpp",

@@ -214,6 +214,13 @@ def test_tuner_roundtrip(tmp_path):
     cli = Tuner.load(str(cli_out)).table                                    # + fallback rows for 2 ranks
     want = json.loads(json.dumps(t.table))
     assert all(cli[op][w] == want[op][w] for op in want for w in want[op]) and "2" in cli["all_reduce"]
+    # a later, partial re-measurement in bf16: the fastest record of a point counts, for fp32 too when asked
+    again2 = tmp_path / "again.jsonl"
+    again2.write_text(json.dumps(dict(op="all_reduce", impl="penny", algo="oneshot_ll", world=4, dtype="bf16", bytes=4096,
+                                      t_us=9, t_graph_us=2)))
+    t2 = Tuner.from_sweep([str(p)], both_dtypes=[str(again2)])
+    assert t2.pick("all_reduce", 4096, 4, "fp32") == "oneshot_ll" and t2.pick("all_reduce", 4096, 4, "bf16") == "oneshot_ll"
+    assert Tuner.from_sweep([str(p), str(again2)]).pick("all_reduce", 4096, 4, "fp32") == "oneshot"
     empty = tmp_path / "empty.jsonl"
     empty.write_text("")
     assert _main([str(empty), "--out", str(tmp_path / "none.json")]) == 1
