@@ -60,6 +60,8 @@ def main():
     add_args(ap)
     args = ap.parse_args()
     rank, world, comm = initialize_distributed(heap_bytes=3 << 30)
+    if comm is None or world < 2:
+        raise SystemExit("expert parallelism needs >= 2 ranks: launch with torchrun --nproc-per-node N")
     run(rank, world, comm, args)
     shutdown()
 
