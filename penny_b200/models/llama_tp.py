@@ -156,14 +156,15 @@ class LlamaTPDecoder:
         self._host_in = torch.zeros(B, dtype=torch.int64).pin_memory()
         self._host_out = torch.zeros(B, dtype=torch.int64).pin_memory()
         # kernels of this library launched per step (the few torch glue ops excluded)
-        chunks = -(-B // 128)  # the decode GEMM takes up to 128 rows per launch
-        gemms = 4 * chunks if linears == "penny" else 0
-        per_layer = gemms + 1 + (1 if linears == "cublas" else 0)  # + fused attention (+ silu*mul beside cuBLAS)
+        chunks = -(-B // 1024)  # the decode GEMM takes up to 1024 rows per launch
+        gemms = 4 * chunks if self.linears == "penny" else 0
+        per_layer = gemms + 1 + (1 if self.linears == "cublas" else 0)  # + fused attention (+ silu*mul beside cuBLAS)
         norms = 2 * cfg.layers + 1
         if backend == "penny_unfused" and world > 1:
             norms += 2 * cfg.layers  # separate all-reduce kernels
-        self.kernels_per_step = (cfg.layers * per_layer + norms + 1 + (1 if world > 1 else 0)
-                                 + (chunks if linears == "penny" else 0))
+        # + arg-max + sampling tail (+ the all-gather of the ranks' candidates) + LM head
+        self.kernels_per_step = (cfg.layers * per_layer + norms + 2 + (1 if world > 1 else 0)
+                                 + (chunks if self.linears == "penny" else 0))
 
     # ------------------------------------------------------------------ weights
     def _init_weights(self, seed: int, full_init: bool):
