@@ -11,6 +11,7 @@ except where DRAM figures need inputs larger than L2).
     python extra/profile_kernels.py gemm_decode       # decode-batch GEMM: a wide matrix (no cluster) and a narrow one (cluster split-K)
     python extra/profile_kernels.py fused_twoshot     # flag-in-data two-shot all-reduce+RMSNorm, 8 emulated ranks
     python extra/profile_kernels.py collectives       # reduce-scatter / all-gather / all-to-all (push and pipelined), 8 emulated ranks
+    python extra/profile_kernels.py moe               # MoE dispatch + combine (and the routing kernels), 8 emulated ranks
 
 Each prints the CUDA-event time per launch so that the same command line can be
 run plainly first and under `ncu --clock-control none -k regex:<kernel> -c <n>`
@@ -117,6 +118,19 @@ def main():
                              ("all_to_all pipelined", lambda: comm.all_to_all(x, algo="pipelined"))):
                 t = timed(fn)
                 print(f"{name} {n * 2 >> 20} MiB per rank bf16, 8 emulated ranks on one GPU: {t:.1f} us")
+        comm.check()
+        comm.close()
+    elif what == "moe":
+        from penny_b200.models.moe_ep import MoeConfig, MoeEPLayer
+        from penny_b200.parallel.comm import Communicator
+        comm = Communicator.emulated(8, heap_bytes=256 << 20)
+        cfg = MoeConfig(hidden=1024, ffn=2048, experts=8, topk=2)
+        tokens = 1024
+        layer = MoeEPLayer(cfg, comm, tokens)
+        xs = [torch.randn(tokens, cfg.hidden, device="cuda").bfloat16() for _ in range(8)]
+        t = timed(lambda: layer.forward(xs))
+        print(f"MoE EP layer, 8 emulated ranks on one GPU, {tokens} tokens per rank, hidden {cfg.hidden}, "
+              f"ffn {cfg.ffn}: {t:.1f} us per forward (routing + dispatch + expert GEMMs + combine)")
         comm.check()
         comm.close()
     elif what in ("fused", "allreduce"):
