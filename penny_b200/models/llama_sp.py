@@ -177,7 +177,7 @@ class LlamaSPPrefill:
             self._col(self.h, l["wgu"], self.gu)
             self._silu_mul()
             self._row(self.act, l["wd"], self.part)
-            if li + 1 < self.L:
+            if li + 1 < len(self.layers):
                 self._add_rmsnorm(self.part, res, self.layers[li + 1]["norm1"], self.h, res)
             else:
                 res.add_(self.part)
