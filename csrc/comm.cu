@@ -212,7 +212,7 @@ void Communicator::all_reduce(int algo, int dtype, const void* const* in, void* 
     default: per_elem_scratch = 4 * (size_t)es; break;
   }
   size_t budget = std::min(kScratchCap, std::max<size_t>(heap_free_bytes() / 2, (size_t)1 << 20));
-  if (algo == ALGO_NVLS || algo == ALGO_NVLS_ONESHOT) budget = kScratchCap;
+  if (algo == ALGO_NVLS) budget = kScratchCap;  // staging regions are sized per call, not from this budget
   size_t seg = std::max<size_t>(budget / per_elem_scratch / 1024 * 1024, 1024);
   if (n <= seg) {
     run_all_reduce_once(algo, dtype, in, out, n, t, stream);
