@@ -379,10 +379,11 @@ __global__ void __launch_bounds__(256) k_argmax(const __nv_bfloat16* __restrict_
     }
   };
   block_best();  // threads of warp 0 hold the chunk's result
-  unsigned int* counter = workspace + r;
-  float* part_val = reinterpret_cast<float*>(workspace + rows) + (size_t)r * kArgmaxMaxChunks;
-  int* part_idx = reinterpret_cast<int*>(workspace + rows + (size_t)rows * kArgmaxMaxChunks) + (size_t)r * kArgmaxMaxChunks;
-  if (chunks > 1) {
+  if (chunks > 1) {  // (a launch without a workspace has one chunk per row)
+    unsigned int* counter = workspace + r;
+    float* part_val = reinterpret_cast<float*>(workspace + rows) + (size_t)r * kArgmaxMaxChunks;
+    int* part_idx =
+        reinterpret_cast<int*>(workspace + rows + (size_t)rows * kArgmaxMaxChunks) + (size_t)r * kArgmaxMaxChunks;
     if (threadIdx.x == 0) {
       part_val[ch] = best;
       part_idx[ch] = bi;
