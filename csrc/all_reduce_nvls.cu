@@ -9,11 +9,9 @@
 //                 result: each GPU's links carry S/N + S bytes instead of the
 //                 2 * S * (N-1)/N of any peer-to-peer algorithm.  Input and output
 //                 in the heap at the same offset on every rank.
-//   NvlsTwoShotStaged   the same for tensors anywhere in device memory, in one
-//                 kernel: stage the input into this call's scratch half, barrier,
-//                 reduce + multicast into the other part of the half, barrier, copy
-//                 out.  Block b stages, reduces and copies the same positions of
-//                 every rank's chunk, so the barriers stay block-local.
+//                 Tensors elsewhere are staged by the communicator with two copies
+//                 (a variant that staged inside the kernel measured 3-7 us slower
+//                 at 8 ranks than the two copy launches it saved).
 //   NvlsOneShot   stage the input into this call's scratch half, ONE barrier, then
 //                 every rank ld_reduces the whole buffer into its own output.  No
 //                 second barrier: the next call uses the other half, and a rank can
@@ -97,8 +95,6 @@ struct NvlsTwoShot {
 
 // scratch: both halves of [V] staged vectors
 PK_HD size_t nvls_oneshot_scratch_bytes(size_t n, int elem_size) { return 2 * vecs_for(n, elem_size) * 16; }
-// scratch: both halves of ([V] staged input + [V] reduced output)
-PK_HD size_t nvls_staged_scratch_bytes(size_t n, int elem_size) { return 4 * vecs_for(n, elem_size) * 16; }
 
 template <typename T>
 struct NvlsOneShot {
@@ -126,66 +122,6 @@ struct NvlsOneShot {
   }
   static __device__ void run(const CommCtx& c, int rank, const CollArgs& a, const Blk& b) {
     run_collective<NvlsOneShot<T>, CollArgs>(c, rank, a, b);
-  }
-};
-
-template <typename T>
-struct NvlsTwoShotStaged {
-  static __device__ void body(const CommCtx& c, int rank, const CollArgs& a, const Blk& b, u64 seq,
-                              int& s_abort) {
-    constexpr size_t E = 16 / sizeof(T);
-    const T* in = reinterpret_cast<const T*>(a.in);
-    T* out = reinterpret_cast<T*>(a.out);
-    const size_t V = ceil_div(a.n, E);
-    const size_t in_base = scratch_half(a.scratch_off, a.scratch_bytes, seq);
-    const size_t out_base = in_base + V * 16;
-    const size_t stride = (size_t)b.nblocks * b.nthreads;
-    const size_t first = (size_t)b.bid * b.nthreads + threadIdx.x;
-    // position j of EVERY rank's chunk belongs to the same (block, thread) on every rank
-    for (int s = 0; s < c.world; ++s) {
-      const Span sp = split_span(V, c.world, s);
-      const size_t n_s = sp.end - sp.begin;
-      for (size_t j0 = first; j0 < n_s; j0 += kBatch * stride) {
-        V16 r[kBatch];
-#pragma unroll
-        for (int u = 0; u < kBatch; ++u)
-          if (j0 + u * stride < n_s) r[u] = load_user_vec<T>(in, sp.begin + j0 + u * stride, a.n);
-#pragma unroll
-        for (int u = 0; u < kBatch; ++u)
-          if (j0 + u * stride < n_s) st16(c.heap[rank] + in_base + (sp.begin + j0 + u * stride) * 16, r[u]);
-      }
-    }
-    PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 1), s_abort);
-    if (s_abort) return;
-    const Span mine = split_span(V, c.world, rank);
-    const size_t len = mine.end - mine.begin;
-    for (size_t j0 = first; j0 < len; j0 += kBatch * stride) {
-      V16 r[kBatch];
-#pragma unroll
-      for (int u = 0; u < kBatch; ++u)
-        if (j0 + u * stride < len) r[u] = multimem_ld_reduce<T>(c.mc + in_base + (mine.begin + j0 + u * stride) * 16);
-#pragma unroll
-      for (int u = 0; u < kBatch; ++u)
-        if (j0 + u * stride < len) multimem_st(c.mc + out_base + (mine.begin + j0 + u * stride) * 16, r[u]);
-    }
-    PK_BLOCK_BARRIER(c, rank, CH_BARRIER, b, flag_value(seq, 2), s_abort);
-    if (s_abort) return;
-    for (int s = 0; s < c.world; ++s) {
-      const Span sp = split_span(V, c.world, s);
-      const size_t n_s = sp.end - sp.begin;
-      for (size_t j0 = first; j0 < n_s; j0 += kBatch * stride) {
-        V16 r[kBatch];
-#pragma unroll
-        for (int u = 0; u < kBatch; ++u)
-          if (j0 + u * stride < n_s) r[u] = ld16(c.heap[rank] + out_base + (sp.begin + j0 + u * stride) * 16);
-#pragma unroll
-        for (int u = 0; u < kBatch; ++u)
-          if (j0 + u * stride < n_s) store_user_vec<T>(out, sp.begin + j0 + u * stride, a.n, r[u]);
-      }
-    }
-  }
-  static __device__ void run(const CommCtx& c, int rank, const CollArgs& a, const Blk& b) {
-    run_collective<NvlsTwoShotStaged<T>, CollArgs>(c, rank, a, b);
   }
 };
 
@@ -237,7 +173,6 @@ static bool nvls_ok(const CommCtx& c, const LaunchCfg& cfg) {
 }
 
 size_t nvls_oneshot_scratch(size_t n, int elem_size) { return nvls_oneshot_scratch_bytes(n, elem_size); }
-size_t nvls_staged_scratch(size_t n, int elem_size) { return nvls_staged_scratch_bytes(n, elem_size); }
 
 cudaError_t launch_all_reduce_nvls(int dtype, int kind, const CommCtx& c, const CollArgs* a,
                                    const LaunchCfg& cfg) {
@@ -246,9 +181,8 @@ cudaError_t launch_all_reduce_nvls(int dtype, int kind, const CommCtx& c, const 
     return cudaErrorNotSupported;
   cudaError_t rc = cudaErrorInvalidValue;
   PENNY_DISPATCH_DTYPE(dtype, T, {
-    rc = kind == NVLS_ONESHOT   ? launch_body<NvlsOneShot<T>, CollArgs>(c, a, cfg)
-         : kind == NVLS_STAGED ? launch_body<NvlsTwoShotStaged<T>, CollArgs>(c, a, cfg)
-                               : launch_body<NvlsTwoShot<T>, CollArgs>(c, a, cfg);
+    rc = kind == NVLS_ONESHOT ? launch_body<NvlsOneShot<T>, CollArgs>(c, a, cfg)
+                              : launch_body<NvlsTwoShot<T>, CollArgs>(c, a, cfg);
   });
   return rc;
 }

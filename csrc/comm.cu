@@ -23,10 +23,8 @@ void ckrt(cudaError_t r, const char* what) {
   }
 }
 constexpr size_t kScratchCap = (size_t)512 << 20;  // a single call never asks for more
-// Switch all-reduce of tensors outside the heap: up to this size the staging copies run inside the
-// kernel (one launch instead of three); above it the copy engines' rate wins.
-constexpr size_t kNvlsStageInKernelBytes = (size_t)1 << 20;
-// ... and from this size the staging copies are pipelined against the reduction, piece by piece
+// Switch all-reduce of tensors outside the heap: from this size the staging copies are pipelined
+// against the reduction, piece by piece
 constexpr size_t kNvlsPipelineBytes = (size_t)256 << 20;  // below, the extra launches and events cost more than the overlap saves (measured)
 constexpr int kNvlsPipePieces = 4;
 }  // namespace
@@ -327,14 +325,8 @@ void Communicator::run_all_reduce_once(int algo, int dtype, const void* const* i
         rc = launch_all_reduce_nvls(dtype, NVLS_TWOSHOT, ctx_, a, cfg_for(ceil_div(V, world_), t, stream, 64, 1));
         break;
       }
-      if (bytes <= kNvlsStageInKernelBytes) {
-        // tensors outside the heap, small enough that two extra copy launches would cost more than
-        // copying inside the kernel: one launch, staged through this call's scratch half
-        set_scratch(ensure(scratch_, nvls_staged_scratch(n, es), "NVLS staged"));
-        rc = launch_all_reduce_nvls(dtype, NVLS_STAGED, ctx_, a, cfg_for(V, t, stream, 64, 1, 2));  // sized for the copies
-        break;
-      }
-      // large: the copy engines' rate matters more than two launches
+      // tensors outside the heap: one copy in, one copy out (copying inside the kernel was measured
+      // slower at 8 ranks: 19.3 vs 16.1 us at 1 KiB, 24.5 vs 17.4 us at 256 KiB, in a graph)
       const size_t in_off0 = in_heap ? a[0].in_heap_off : ensure(stage_in_, bytes, "NVLS input staging").off;
       const size_t out_off0 = out_heap ? out_off : ensure(stage_out_, bytes, "NVLS output staging").off;
       if (bytes < kNvlsPipelineBytes) {

@@ -92,9 +92,8 @@ cudaError_t launch_all_to_all_pipelined(int dtype, const CommCtx& c, const CollA
                                         const LaunchCfg& cfg);
 // NVLS (multimem) family: real launches only, c.mc must be set, tensors in the heap.
 // kind: which switch all-reduce kernel
-enum { NVLS_TWOSHOT = 0, NVLS_ONESHOT = 1, NVLS_STAGED = 2 };
+enum { NVLS_TWOSHOT = 0, NVLS_ONESHOT = 1 };
 size_t nvls_oneshot_scratch(size_t n, int elem_size);  // scratch bytes of NVLS_ONESHOT
-size_t nvls_staged_scratch(size_t n, int elem_size);   // ... of NVLS_STAGED
 cudaError_t launch_all_reduce_nvls(int dtype, int kind, const CommCtx& c, const CollArgs* a,
                                    const LaunchCfg& cfg);
 cudaError_t launch_reduce_scatter_nvls(int dtype, const CommCtx& c, const CollArgs* a,
