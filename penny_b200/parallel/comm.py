@@ -248,9 +248,9 @@ class Communicator:
 
         The switch algorithms take tensors anywhere in device memory: "nvls_oneshot" stages its input
         inside the kernel (one flag exchange, every rank pulls the whole sum; in place is fine);
-        "nvls" reduces and multicasts in place for tensors from `empty()`, stages inside the kernel
-        up to 1 MiB, with two copies above that and, from 256 MiB, with the copies of piece i + 1 and
-        piece i - 1 running on side streams under the reduction of piece i."""
+        "nvls" reduces and multicasts in place for tensors from `empty()`, goes through two staging
+        copies for other tensors and, from 256 MiB, runs the copies of piece i + 1 and piece i - 1 on
+        side streams under the reduction of piece i."""
         ins = self._as_list(inp)
         outs = self._as_list(out) if out is not None else [torch.empty_like(x) for x in ins]
         if algo == "auto" and os.environ.get("PENNY_ALGO"):
