@@ -274,7 +274,7 @@ def test_poisoned_scratch_never_reaches_a_result():
         comm.close()
 
 
-@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("world", [2, 8])
 def test_gemm_push_into_ll_twoshot_fused_norm(comms, world):
     """A row-parallel decode GEMM whose epilogue writes the rows other ranks own straight into their
     flag-in-data receive lines, followed by the all-reduce + RMSNorm that only polls: same result as the
