@@ -224,3 +224,38 @@ def test_tuner_roundtrip(tmp_path):
     empty = tmp_path / "empty.jsonl"
     empty.write_text("")
     assert _main([str(empty), "--out", str(tmp_path / "none.json")]) == 1
+
+
+def test_builtin_tuner_table_names_are_known():
+    """Every algorithm the shipped table can hand out is a name the API it is handed to accepts."""
+    from penny_b200.parallel.tuner import BUILTIN_PATH, Tuner
+    t = Tuner.load(BUILTIN_PATH)
+    assert t.source == BUILTIN_PATH
+    known = {
+        "all_reduce": {"oneshot", "oneshot_ll", "twoshot", "nvls", "nvls_oneshot", "ring_simple", "ring_standard",
+                       "double_ring", "tree"},
+        "reduce_scatter": {"push", "pipelined", "nvls"},
+        "all_gather": {"push", "nvls"},
+        "all_to_all": {"push", "pipelined"},
+        "fused_norm": {"ll", "ll_twoshot", "flag", "nvls", "nvls_oneshot"},
+    }
+    seen_worlds = set()
+    for op, per_world in t.table.items():
+        assert op in known, op
+        for world, per_dt in per_world.items():
+            seen_worlds.add(int(world))
+            for dt, per_mem in per_dt.items():
+                assert dt in ("bf16", "fp32", "fp16"), dt
+                for mem, rows in per_mem.items():
+                    assert mem in ("sym", "any") and rows and rows[-1][0] is None
+                    bounds = [b for b, _ in rows[:-1]]
+                    assert bounds == sorted(bounds)
+                    for _, algo in rows:
+                        assert algo in known[op], (op, world, dt, mem, algo)
+    assert {2, 8} <= seen_worlds
+    # sizes between, below and above the measured points all resolve
+    for world in (2, 4, 8):
+        for nbytes in (1, 4096, 3 << 20, 5 << 30):
+            for sym in (False, True):
+                assert t.pick("all_reduce", nbytes, world, "bf16", symmetric=sym) in known["all_reduce"]
+                assert t.pick("all_reduce", nbytes, world, torch.float32, symmetric=sym) in known["all_reduce"]
