@@ -71,7 +71,11 @@ __global__ void __launch_bounds__(kRouteThreads) k_moe_tables(const int* __restr
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int e = threadIdx.x; e < experts; e += blockDim.x) hist[e] = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < pairs; i += blockDim.x) atomicAdd(&hist[ids[i]], 1);
+  // ids outside [0, experts) are left out of every table (they would index past the histogram)
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = ids[i];
+    if ((unsigned)e < (unsigned)experts) atomicAdd(&hist[e], 1);
+  }
   __syncthreads();
   if (threadIdx.x == 0) {
     int run = 0;
@@ -89,8 +93,9 @@ __global__ void __launch_bounds__(kRouteThreads) k_moe_tables(const int* __restr
     for (int i = threadIdx.x; i < kRouteWarps * experts; i += blockDim.x) warp_cnt[i] = 0;
     __syncthreads();
     const int p = base + threadIdx.x;
-    const bool live = p < pairs;
-    const int e = live ? ids[p] : -1 - lane;  // dead lanes never match anyone
+    const int id = p < pairs ? ids[p] : -1;
+    const bool live = (unsigned)id < (unsigned)experts;
+    const int e = live ? id : -1 - lane;  // dead lanes never match anyone
     const unsigned same = __match_any_sync(0xffffffffu, e);
     const int rank_in_warp = __popc(same & ((1u << lane) - 1u));
     if (live && rank_in_warp == 0) warp_cnt[warp * experts + e] = __popc(same);
