@@ -259,3 +259,32 @@ def test_builtin_tuner_table_names_are_known():
             for sym in (False, True):
                 assert t.pick("all_reduce", nbytes, world, "bf16", symmetric=sym) in known["all_reduce"]
                 assert t.pick("all_reduce", nbytes, world, torch.float32, symmetric=sym) in known["all_reduce"]
+
+
+def test_tuner_picks_the_fastest_measured_algorithm(tmp_path):
+    """Property: with tolerance 0, at every measured size `pick` returns an algorithm whose time
+    equals the minimum over the algorithms measured at that size (ties may go either way), and
+    between two measured sizes it returns the choice of the next larger one."""
+    import json
+    import random
+    from penny_b200.parallel.tuner import Tuner
+    rng = random.Random(7)
+    algos = ["oneshot_ll", "oneshot", "twoshot", "nvls"]
+    for trial in range(20):
+        sizes = sorted(rng.sample([1 << p for p in range(10, 31)], rng.randint(2, 8)))
+        recs, best = [], {}
+        for sz in sizes:
+            times = {a: rng.uniform(5, 500) for a in rng.sample(algos, rng.randint(1, 4))}
+            best[sz] = times
+            for a, t in times.items():
+                recs.append(dict(op="all_reduce", impl="penny", algo=a, world=8, dtype="bf16", bytes=sz, t_us=t))
+        rng.shuffle(recs)
+        path = tmp_path / f"s{trial}.jsonl"
+        path.write_text("\n".join(json.dumps(r) for r in recs))
+        t = Tuner.from_sweep(str(path), tolerance=0.0)
+        for i, sz in enumerate(sizes):
+            got = t.pick("all_reduce", sz, 8, "bf16")
+            assert best[sz][got] == min(best[sz].values())
+            if i + 1 < len(sizes) and sizes[i + 1] > sz + 1:
+                assert t.pick("all_reduce", sz + 1, 8, "bf16") == t.pick("all_reduce", sizes[i + 1], 8, "bf16")
+        assert t.pick("all_reduce", sizes[-1] * 4, 8, "bf16") == t.pick("all_reduce", sizes[-1], 8, "bf16")
