@@ -201,3 +201,16 @@ def test_bench_clock_sampler_against_fake_nvml(monkeypatch):
     s2.start()
     time.sleep(0.03)
     assert s2.stop()["reasons"] == ["hw_slowdown", "hw_thermal_slowdown"]
+
+
+def test_attention_split_rule_reproduces_the_measured_choices():
+    """The split rule of the decode attention is a fit to measurements; the points it was fitted to."""
+    from penny_b200.models.llama_tp import LlamaTPDecoder
+    f = LlamaTPDecoder.attention_splits
+    assert f(64, 2112) == 4       # TP 8, batch 64: 256 CTAs in one wave beat 320 in two (14.7 vs 20.8 us in the step)
+    assert f(512, 2112) == 1      # TP 1, batch 64: 512 long CTAs beat 2048 short ones (83.7 vs 92.6 us)
+    assert f(8, 2112) >= 8        # a handful of rows: as many splits as still pay their fixed cost
+    for items in (1, 3, 64, 100, 512, 4096):
+        for kv in (16, 2048, 32768):
+            s = f(items, kv)
+            assert 1 <= s <= 16
